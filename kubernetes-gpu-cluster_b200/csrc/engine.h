@@ -77,6 +77,22 @@ struct HybridLayerW {
   HybMat up, down, router, s_gate, s_up, s_down;
   void *e_gate = nullptr, *e_up = nullptr, *e_down = nullptr;
   int64_t state_off = 0;                      // floats from the start of a state slot to this layer's state
+  // WKV mixer: the five blend vectors [5, d] (r, k, v, g, w), the four projections stacked [4, heads * dim, d], the
+  // decay's low-rank pair (w2 carries the decay's bias), the bonus u (fp32 [heads * dim]) and the per-head output norm
+  void* wkv_mu = nullptr;
+  HybMat wkv_rkvg, wkv_w1, wkv_w2;
+  float* wkv_u = nullptr;
+  void* wkv_norm = nullptr;
+  // latent attention: `proj` holds [dq | dkv] or [q | dkv | g] (column offsets lat_dkv, lat_g), the latents' norm
+  // weights, the query up-projection and the stacked key / value up-projections [uk | uv]
+  HybMat lat_uq, lat_ukv;
+  void *lat_qnorm = nullptr, *lat_kvnorm = nullptr;
+  int lat_dkv = 0, lat_g = 0;
+  // dense clamped gated unit: [gate | up] rows in one block (`up` names the second half)
+  void* ff_gate = nullptr;
+  // hyper-connected residual, per sublayer (0: mixer, 1: feed-forward), fp32 on the device: read weights [S], write
+  // weights [S], mix matrix [S, S] (from, to), and the per-column scale of the sublayer's result [d]; null = ones / identity
+  float *hc_in[2] = {nullptr, nullptr}, *hc_out[2] = {nullptr, nullptr}, *hc_mix[2] = {nullptr, nullptr}, *col_scale[2] = {nullptr, nullptr};
 };
 
 // Per-step metadata, laid out once in pinned host memory and mirrored on the device with the
@@ -100,6 +116,10 @@ struct kge_engine {
   // layer-list ("hybrid") models: fp32 residual stream, their own activation arena and the recurrent-state pool
   std::vector<kge::HybridLayerW> hyb;
   float *res32 = nullptr, *gates32 = nullptr, *logits32 = nullptr, *state = nullptr, *mo32 = nullptr;
+  float* y32 = nullptr;                      // [tokens, d]: a sublayer's sum when it has more sources than one combine pass takes
+  void* embed_norm_w = nullptr;              // weight of the norm the embedding goes through (models that have one)
+  void *mixes = nullptr, *rkvg = nullptr;    // WKV: the blended inputs [5, tokens, d] and the projections [4, tokens, heads * dim]
+  void *latq = nullptr, *latc = nullptr, *latkv = nullptr, *qbuf = nullptr;   // latent attention: normed latents, [k | v] up-projections, queries
   void *hx = nullptr, *pbuf = nullptr, *ubuf = nullptr, *mixbuf = nullptr, *obuf1 = nullptr, *obuf2 = nullptr, *ffbuf = nullptr;
   void *moe_hidden = nullptr, *moe_out = nullptr, *hsel = nullptr, *moe_xperm = nullptr, *moe_operm = nullptr;
   int32_t* moe_tile_group = nullptr;         // expert of every 256-row tile of the padded routed rows (prompt steps)

@@ -83,6 +83,14 @@ struct HB {
     if (!dummy() && !stack({name}, {n}, 1, &v)) return nullptr;
     return upload_raw(v);
   }
+  // a vector that a checkpoint may leave out (null then: the caller's default); without a checkpoint the given values
+  float* opt_f32(const std::string& name, int64_t n, const std::vector<float>& dummy_v, bool* failed) {
+    if (dummy()) return dummy_v.empty() ? nullptr : upload_raw(dummy_v);
+    if (!md->find(name)) return nullptr;
+    std::vector<float> v;
+    if (!stack({name}, {n}, 1, &v)) { *failed = true; return nullptr; }
+    return upload_raw(v);
+  }
   // tensors stacked along their first dimension; every one must have `inner` elements per leading index
   bool stack(const std::vector<std::string>& names, const std::vector<int64_t>& lead, int64_t inner, std::vector<float>* out) {
     out->clear();
@@ -131,22 +139,28 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
 #define HB_OK(p) do { if (!(p)) return fail(b.err); } while (0)
   HB_OK(e->embed = (bf16*)b.mat({"embed"}, {s.vocab}, d, ws));
   HB_OK(e->lm_head = (bf16*)b.mat({"head"}, {s.vocab}, d, ws));
-  HB_OK(e->final_w = (bf16*)b.mat({"final.norm"}, {d}, 1, 0.f, s.hyb_layernorm ? 1.f : 0.f));
+  const bool plain_norm_w = s.hyb_layernorm || s.streams > 0;      // the norm weight multiplies as it is (else it is applied as 1 + w)
+  HB_OK(e->final_w = (bf16*)b.mat({"final.norm"}, {d}, 1, 0.f, plain_norm_w ? 1.f : 0.f));
+  if (s.embed_norm) HB_OK(e->embed_norm_w = b.mat({"embed.norm"}, {d}, 1, 0.f, 1.f));
   e->hyb.resize(s.L);
   int64_t state_floats = 0;
   int max_mo = 1;
   int max_proj = 1, max_mix = 1, max_ff = 1, max_gate = 1, max_u = 1, max_top = 0, max_eff = 1, max_E = 1;
+  int max_hd = 0, max_qr = 0, max_kvr = 0, max_lkv = 0, max_lq = 0;      // WKV heads * dim; latent ranks, [k | v] and query widths
   for (int i = 0; i < s.L; ++i) {
     const HybridLayerSpec& h = s.hybrid[i];
     HybridLayerW& L = e->hyb[i];
-    const std::string p = "l" + std::to_string(i) + ".", mx = p + "mix.", fp = p + "mlp.";
-    if (h.weights_of >= 0) {                   // another layer's tensors; the paged caches below stay this layer's own
+    const std::string p = "l" + std::to_string(h.tensor_index >= 0 ? h.tensor_index : i) + ".", mx = p + "mix.", fp = p + "mlp.";
+    if (h.weights_of >= 0) {                   // another layer's tensors; the paged caches below and the state stay this layer's own
       L = e->hyb[h.weights_of];
       L.kc = L.vc = nullptr;
       L.state_off = state_floats;
+      if (h.mixer == HybridLayerSpec::RGLRU) state_floats += rglru_state_floats(h.width, h.conv);
+      else if (h.mixer == HybridLayerSpec::PARALLEL) state_floats += mlstm_state_floats(h.m_heads, h.m_dim, h.m_vdim);
+      else if (h.mixer == HybridLayerSpec::WKV) state_floats += wkv_state_floats(d, h.heads, h.dim);
       continue;
     }
-    const float norm_one = s.hyb_layernorm ? 1.f : 0.f;      // the weight that leaves the normed row as it is
+    const float norm_one = plain_norm_w ? 1.f : 0.f;      // the weight that leaves the normed row as it is
     HB_OK(L.norm1 = b.mat({p + "norm1"}, {d}, 1, 0.f, norm_one));
     if (s.hyb_prenorm_pair && h.mlp != HybridLayerSpec::NONE) HB_OK(L.norm2 = b.mat({p + "norm2"}, {d}, 1, 0.f, norm_one));
     L.state_off = state_floats;
@@ -185,6 +199,52 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
       L.o.N = d; L.o.K = h.heads * h.vdim;
       HB_OK(L.o.w = b.mat({mx + "o"}, {d}, h.heads * h.vdim, ws));
       max_proj = std::max(max_proj, L.qk.N); max_mix = std::max(max_mix, L.o.K);
+    } else if (h.mixer == HybridLayerSpec::WKV) {
+      const int hd = h.heads * h.dim;
+      int lr = h.decay_rank;
+      if (!b.dummy()) {
+        const HostTensor* t1 = md.find(mx + "w1");
+        if (!t1 || t1->shape.size() != 2) return fail("missing tensor " + mx + "w1");
+        lr = (int)t1->shape[0];
+      } else if (lr <= 0) lr = 64;
+      HB_OK(L.wkv_mu = b.mat({mx + "mu.r", mx + "mu.k", mx + "mu.v", mx + "mu.g", mx + "mu.w"}, {d, d, d, d, d}, 1, 0.f, 0.5f));
+      L.wkv_rkvg.N = hd; L.wkv_rkvg.K = d;
+      HB_OK(L.wkv_rkvg.w = b.mat({mx + "r", mx + "k", mx + "v", mx + "g"}, {hd, hd, hd, hd}, d, ws));
+      L.wkv_w1.N = lr; L.wkv_w1.K = d; L.wkv_w2.N = hd; L.wkv_w2.K = lr;
+      HB_OK(L.wkv_w1.w = b.mat({mx + "w1"}, {lr}, d, ws));
+      HB_OK(L.wkv_w2.w = b.mat({mx + "w2"}, {hd}, lr, ws));
+      HB_OK(L.wkv_w2.b = b.mat({mx + "w0"}, {hd}, 1, 0.f, -1.f));
+      HB_OK(L.wkv_u = b.vec_f32(mx + "u", hd, 0.5f));
+      HB_OK(L.wkv_norm = b.mat({mx + "norm"}, {hd}, 1, 0.f, 1.f));
+      L.o.N = d; L.o.K = hd;
+      HB_OK(L.o.w = b.mat({mx + "o"}, {d}, hd, ws));
+      state_floats += wkv_state_floats(d, h.heads, h.dim);
+      max_hd = std::max(max_hd, hd); max_mix = std::max(max_mix, hd); max_gate = std::max(max_gate, hd); max_mo = std::max(max_mo, hd); max_u = std::max(max_u, lr);
+    } else if (h.mixer == HybridLayerSpec::LATENT) {
+      const int nope = h.dim - h.rot_part, nq = h.heads * h.dim, nkv = h.kv_rank + h.rot_part, nv = h.heads * h.vdim;
+      if (h.q_rank > 0) {
+        L.lat_dkv = h.q_rank; L.proj.N = h.q_rank + nkv; L.proj.K = d;
+        HB_OK(L.proj.w = b.mat({mx + "dq", mx + "dkv"}, {h.q_rank, nkv}, d, ws));
+        HB_OK(L.lat_qnorm = b.mat({mx + "dq.norm"}, {h.q_rank}, 1, 0.f, 1.f));
+        L.lat_uq.N = nq; L.lat_uq.K = h.q_rank;
+        HB_OK(L.lat_uq.w = b.mat({mx + "uq"}, {nq}, h.q_rank, ws * 4));
+      } else {
+        L.lat_dkv = nq; L.lat_g = nq + nkv; L.proj.N = nq + nkv + (h.out_gate ? nv : 0); L.proj.K = d;
+        if (h.out_gate) HB_OK(L.proj.w = b.mat({mx + "q", mx + "dkv", mx + "g"}, {nq, nkv, nv}, d, ws));
+        else HB_OK(L.proj.w = b.mat({mx + "q", mx + "dkv"}, {nq, nkv}, d, ws));
+      }
+      HB_OK(L.lat_kvnorm = b.mat({mx + "dkv.norm"}, {h.kv_rank}, 1, 0.f, 1.f));
+      L.lat_ukv.N = h.heads * nope + nv; L.lat_ukv.K = h.kv_rank;
+      HB_OK(L.lat_ukv.w = b.mat({mx + "uk", mx + "uv"}, {h.heads * nope, nv}, h.kv_rank, ws * 4));
+      if (h.rot_dims > 0) {
+        std::vector<double> fr((size_t)h.rot_dims / 2);
+        rotary_frequencies(h.rot_dims, h.rot_base, 0.0, 0.0, 32.0, 1.0, fr.data(), &L.rot_mult);
+        HB_OK(L.rot_freq = b.upload_raw(fr));
+      }
+      L.o.N = d; L.o.K = nv;
+      HB_OK(L.o.w = b.mat({mx + "o"}, {d}, nv, ws));
+      max_proj = std::max(max_proj, L.proj.N); max_mix = std::max(max_mix, nv);
+      max_qr = std::max(max_qr, h.q_rank); max_kvr = std::max(max_kvr, h.kv_rank); max_lkv = std::max(max_lkv, L.lat_ukv.N); max_lq = std::max(max_lq, nq);
     } else {
       const int nq = h.heads * h.dim, nk = h.kv_heads * h.dim, nv = h.kv_heads * h.vdim, mq = h.m_heads * h.m_dim, mv = h.m_heads * h.m_vdim;
       L.off_k = nq; L.off_v = nq + nk; L.off_mq = L.off_v + nv; L.off_mk = L.off_mq + mq; L.off_mv = L.off_mk + mq; L.off_mg = L.off_mv + mv;
@@ -212,7 +272,28 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
       max_mo = std::max(max_mo, mv);
       max_proj = std::max(max_proj, L.proj.N); max_mix = std::max(max_mix, ko); max_gate = std::max(max_gate, 2 * h.m_heads);
     }
-    if (h.mlp == HybridLayerSpec::DENSE) {
+    if (s.streams > 0) {
+      // the hyper-connection tensors and the per-column scales of both sublayers (a checkpoint without them: plain sums)
+      const int S = s.streams;
+      bool bad = false;
+      for (int q = 0; q < (h.mlp == HybridLayerSpec::NONE ? 1 : 2); ++q) {
+        const std::string hc = p + "hc" + std::to_string(q + 1) + ".";
+        std::vector<float> din((size_t)S, 1.f / S), dout((size_t)S, 1.f), dmix((size_t)S * S, 0.f), dls((size_t)d, 1.f);
+        for (int a1 = 0; a1 < S; ++a1) for (int a2 = 0; a2 < S; ++a2) dmix[(size_t)a1 * S + a2] = a1 == a2 ? 0.75f : 0.25f / std::max(S - 1, 1);
+        L.hc_in[q] = b.opt_f32(hc + "in", S, din, &bad);
+        L.hc_out[q] = b.opt_f32(hc + "out", S, dout, &bad);
+        L.hc_mix[q] = b.opt_f32(hc + "mix", (int64_t)S * S, dmix, &bad);
+        L.col_scale[q] = b.opt_f32(p + "ls" + std::to_string(q + 1), d, dls, &bad);
+        if (bad || !b.err.empty()) return fail(b.err);
+      }
+    }
+    if (h.mlp == HybridLayerSpec::DENSE && h.ff_limit > 0.f) {
+      L.up.N = h.ff; L.up.K = d; L.down.N = d; L.down.K = h.ff;
+      HB_OK(L.ff_gate = b.mat({fp + "gate", fp + "up"}, {h.ff, h.ff}, d, ws));
+      L.up.w = (uint8_t*)L.ff_gate + (int64_t)h.ff * d * b.esz();
+      HB_OK(L.down.w = b.mat({fp + "down"}, {d}, h.ff, ws));
+      max_ff = std::max(max_ff, h.ff);
+    } else if (h.mlp == HybridLayerSpec::DENSE) {
       L.up.N = h.ff; L.up.K = d; L.down.N = d; L.down.K = h.ff;
       HB_OK(L.up.w = b.mat({fp + "up"}, {h.ff}, d, ws));
       HB_OK(L.down.w = b.mat({fp + "down"}, {d}, h.ff, ws));
@@ -223,10 +304,15 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
       if (h.router_bias) HB_OK(L.router_b = b.mat({fp + "router.b"}, {h.experts}, 1, 0.f, 0.f));
       // per expert [gate | up] rows in one block (what the fused gated GEMM reads), then all experts' down matrices
       std::vector<std::string> gu, dn;
-      std::vector<int64_t> lf((size_t)2 * h.experts, h.expert_ff), ld((size_t)h.experts, d);
-      for (int x = 0; x < h.experts; ++x) { const std::string ep = fp + "e" + std::to_string(x) + "."; gu.push_back(ep + "gate"); gu.push_back(ep + "up"); dn.push_back(ep + "down"); }
+      const bool gated = h.glu != HybridLayerSpec::GLU_NONE_RELU2;      // an ungated expert has one front matrix: [E, ff, d]
+      std::vector<int64_t> lf((size_t)(gated ? 2 : 1) * h.experts, h.expert_ff), ld((size_t)h.experts, d);
+      for (int x = 0; x < h.experts; ++x) {
+        const std::string ep = fp + "e" + std::to_string(x) + ".";
+        if (gated) gu.push_back(ep + "gate");
+        gu.push_back(ep + "up"); dn.push_back(ep + "down");
+      }
       HB_OK(L.e_gate = b.mat(gu, lf, d, ws));
-      L.e_up = (uint8_t*)L.e_gate + (int64_t)h.expert_ff * d * b.esz();
+      L.e_up = gated ? (uint8_t*)L.e_gate + (int64_t)h.expert_ff * d * b.esz() : nullptr;
       HB_OK(L.e_down = b.mat(dn, ld, h.expert_ff, ws));
       if (h.shared_ff > 0) {
         L.s_gate.N = L.s_up.N = h.shared_ff; L.s_gate.K = L.s_up.K = d; L.s_down.N = d; L.s_down.K = h.shared_ff;
@@ -250,7 +336,17 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   e->ld_logits = e->hyb_head_tc ? s.vocab : (int)align_up64(s.vocab, 64);
   e->vocab_shard = e->vocab_loc = s.vocab; e->vocab_col0 = 0;
   auto aalloc = [&](int64_t elems, int esz) -> void* { return b.dalloc(elems, esz); };
-  e->res32 = (float*)aalloc((int64_t)Tm * d, 4);
+  e->res32 = (float*)aalloc((int64_t)Tm * d * std::max(s.streams, 1), 4);
+  if (s.streams > 0) { e->y32 = (float*)aalloc((int64_t)Tm * d, 4); if (!e->y32) return fail(b.err); }
+  if (max_hd > 0) {
+    e->mixes = aalloc((int64_t)5 * Tm * d, es); e->rkvg = aalloc((int64_t)4 * Tm * max_hd, es);
+    if (!e->mixes || !e->rkvg) return fail(b.err);
+  }
+  if (max_lkv > 0) {
+    e->latq = aalloc((int64_t)Tm * std::max(max_qr, 1), es); e->latc = aalloc((int64_t)Tm * max_kvr, es);
+    e->latkv = aalloc((int64_t)Tm * max_lkv, es); e->qbuf = aalloc((int64_t)Tm * max_lq, es);
+    if (!e->latq || !e->latc || !e->latkv || !e->qbuf) return fail(b.err);
+  }
   e->hx = aalloc((int64_t)Tm * d, es);
   e->pbuf = aalloc((int64_t)Tm * max_proj, es);
   e->ubuf = aalloc((int64_t)Tm * max_u, es);
@@ -317,7 +413,7 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   // paged caches of the attention sides: K [blocks, G, block_size, dim], V [blocks, G, block_size, vdim] per layer
   int64_t blk_bytes = 0;
   for (auto& h : s.hybrid)
-    if (h.mixer != HybridLayerSpec::RGLRU) blk_bytes += (int64_t)h.kv_heads * e->cfg.block_size * (h.dim + h.vdim) * es;
+    if (h.has_cache()) blk_bytes += (int64_t)h.kv_heads * e->cfg.block_size * (h.dim + h.vdim) * es;
   int nb = e->cfg.num_blocks;
   if (nb <= 0) {
     const int64_t cap = (int64_t)e->cfg.max_num_seqs * e->max_blocks_per_seq + 1;
@@ -338,7 +434,7 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   e->kv_bytes = blk_bytes * nb;
   for (int i = 0; i < s.L; ++i) {
     const HybridLayerSpec& h = s.hybrid[i];
-    if (h.mixer == HybridLayerSpec::RGLRU) continue;
+    if (!h.has_cache()) continue;
     const int64_t nk = (int64_t)nb * h.kv_heads * e->cfg.block_size * h.dim, nv = (int64_t)nb * h.kv_heads * e->cfg.block_size * h.vdim;
     e->hyb[i].kc = aalloc(nk, es); e->hyb[i].vc = aalloc(nv, es);
     if (!e->hyb[i].kc || !e->hyb[i].vc) return fail("KV pool allocation failed");
@@ -414,16 +510,48 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
     return s.hyb_layernorm ? layernorm_f32in(y, e->res32, rows, w, R, d, s.eps, out_scale, elt, st)
                            : rmsnorm_f32in(y, e->res32, rows, w, R, d, s.eps, 1.f, out_scale, elt, st);
   };
-  HFWD(C_EMBED, Td * (es + 4), 0, embed_f32(e->res32, m.ids, e->embed, T, d, elt, st));
+  // hyper-connected residual: S streams per token, read through a sublayer's input weights and a norm, written back
+  // through its mix matrix and output weights; designs with one plain stream keep the residual sum
+  const bool hyper = s.streams > 0;
+  const int S = std::max(s.streams, 1);
+  auto stream_read = [&](void* y, const float* in_w, const int32_t* rows, const void* w, int R, float out_scale, float* sum_out) -> int {
+    StreamNormArgs sn;
+    sn.y = y; sn.xs = e->res32; sn.in_w = in_w; sn.rows = rows; sn.w = w; sn.sum_out = sum_out; sn.R = R; sn.d = d; sn.S = S; sn.eps = s.eps; sn.out_scale = out_scale; sn.elt = elt;
+    return stream_norm(sn, st);
+  };
+  if (hyper) HFWD(C_EMBED, Td * (es + 4.0 * S), 0, embed_norm_streams(e->res32, m.ids, e->embed, s.embed_norm ? e->embed_norm_w : nullptr, T, d, S, s.eps, elt, st));
+  else HFWD(C_EMBED, Td * (es + 4), 0, embed_f32(e->res32, m.ids, e->embed, T, d, elt, st));
   for (int i = 0; i < s.L; ++i) {
     const HybridLayerSpec& h = s.hybrid[i];
     const HybridLayerW& L = e->hyb[i];
-    HFWD(C_NORM, Td * (4 + es), 0, layer_norm(e->hx, nullptr, L.norm1, T, 1.f));
+    if (hyper) HFWD(C_NORM, Td * (4.0 * S + es), 0, stream_read(e->hx, L.hc_in[0], nullptr, L.norm1, T, 1.f, nullptr));
+    else HFWD(C_NORM, Td * (4 + es), 0, layer_norm(e->hx, nullptr, L.norm1, T, 1.f));
     CombineArgs cb;
+    bool y32_used = false;
+    int sub = 0;                                       // the sublayer whose result is being summed (0: mixer, 1: feed-forward)
     auto add_src = [&](const void* p, int ld, float scale, const float* rscale = nullptr, int rs_stride = 0) {
       cb.src[cb.n] = p; cb.ld[cb.n] = ld; cb.scale[cb.n] = scale; cb.rscale[cb.n] = rscale; cb.rs_stride[cb.n] = rs_stride; ++cb.n;
     };
-    auto flush = [&]() -> int { if (cb.n == 0) return 0; int rc = residual_combine(e->res32, cb, T, d, elt, st); cb = CombineArgs(); return rc; };
+    // more sources follow: a plain stream takes them as they come; with several streams they gather in an fp32 row first
+    auto flush_more = [&]() -> int {
+      if (cb.n == 0) return 0;
+      int rc;
+      if (!hyper) rc = residual_combine(e->res32, cb, T, d, elt, st);
+      else {
+        if (!y32_used) { KGE_CUDA_OK(cudaMemsetAsync(e->y32, 0, (size_t)T * d * 4, st)); y32_used = true; }
+        rc = residual_combine(e->y32, cb, T, d, elt, st);
+      }
+      cb = CombineArgs();
+      return rc;
+    };
+    auto flush = [&]() -> int {
+      if (!hyper) return flush_more();
+      StreamCombineArgs sc;
+      sc.xs = e->res32; sc.src = cb; sc.y32 = y32_used ? e->y32 : nullptr; sc.col_scale = L.col_scale[sub]; sc.mix = L.hc_mix[sub]; sc.out_w = L.hc_out[sub];
+      sc.mult = s.residual_mult; sc.T = T; sc.d = d; sc.S = S; sc.elt = elt;
+      cb = CombineArgs(); y32_used = false;
+      return stream_combine(sc, st);
+    };
     if (h.mixer == HybridLayerSpec::RGLRU) {
       const int w = h.width, bw = w / h.blocks;
       DENSE(e->pbuf, 2 * w, e->hx, d, L.yx, T, ACT_NONE);
@@ -477,6 +605,64 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
               : attn_bias_chunk(aa, st));
       DENSE(e->obuf1, d, e->mixbuf, ko, L.o, T, ACT_NONE);
       add_src(e->obuf1, d, 1.f);
+    } else if (h.mixer == HybridLayerSpec::WKV) {
+      const int hd = h.heads * h.dim, lr = L.wkv_w1.N;
+      WkvArgs wa;
+      wa.h = e->hx; wa.ldh = d; wa.mu = L.wkv_mu; wa.mixes = e->mixes; wa.nmix = 5; wa.d = d;
+      wa.state = e->state + L.state_off; wa.slot_stride = e->slot_stride; wa.slots = m.sslot; wa.qsl = m.qsl; wa.positions = m.pos; wa.token_req = m.treq;
+      wa.B = B; wa.T = T; wa.H = h.heads; wa.dim = h.dim; wa.eps = s.eps; wa.elt = elt;
+      HFWD(C_MLSTM, Td * 6 * es, 0, wkv_shift_mix(wa, st));
+      ++e->launches;
+      for (int z = 0; z < 4; ++z) {                      // r, k, v and the gate, each from its own blend
+        HybMat mz; mz.w = at(L.wkv_rkvg.w, (int64_t)z * hd * d); mz.N = hd; mz.K = d;
+        DENSE(at(e->rkvg, (int64_t)z * T * hd), hd, at(e->mixes, (int64_t)z * T * d), d, mz, T, ACT_NONE);
+      }
+      {
+        LinearArgs a1;     // the decay's logit: a low-rank pair with a tanh between, the second half and its bias in fp32
+        a1.x = at(e->mixes, (int64_t)4 * T * d); a1.ldx = d; a1.w = L.wkv_w1.w; a1.y = e->ubuf; a1.ldy = lr; a1.T = T; a1.N = lr; a1.K = d; a1.act = ACT_TANH;
+        a1.elt = elt; a1.out_f32 = e->f32;
+        HFWD(C_MLSTM, es * ((double)lr * d + (double)T * (d + lr)), 2.0 * Td * lr, linear_any(a1, st));
+        LinearArgs a2;
+        a2.x = e->ubuf; a2.ldx = lr; a2.w = L.wkv_w2.w; a2.bias = L.wkv_w2.b; a2.y = e->gates32; a2.ldy = hd; a2.T = T; a2.N = hd; a2.K = lr;
+        a2.elt = elt; a2.out_f32 = true;
+        HFWD(C_MLSTM, es * ((double)lr * hd + (double)T * lr) + 4.0 * T * hd, 2.0 * T * (double)hd * lr, linear_any(a2, st));
+      }
+      wa.r = e->rkvg; wa.k = at(e->rkvg, (int64_t)T * hd); wa.v = at(e->rkvg, (int64_t)2 * T * hd); wa.gate_pre = at(e->rkvg, (int64_t)3 * T * hd); wa.ld = hd;
+      wa.decay_pre = e->gates32; wa.u = L.wkv_u; wa.norm_w = L.wkv_norm; wa.o32 = e->mo32; wa.out = e->mixbuf; wa.ldo = hd;
+      HFWD(C_MLSTM, 2.0 * B * h.heads * (double)h.dim * h.dim * 4 + (double)T * hd * (5 * es + 12), 4.0 * T * h.heads * (double)h.dim * h.dim, wkv_scan(wa, st));
+      ++e->launches;
+      DENSE(e->obuf1, d, e->mixbuf, hd, L.o, T, ACT_NONE);
+      add_src(e->obuf1, d, 1.f);
+    } else if (h.mixer == HybridLayerSpec::LATENT) {
+      const int H = h.heads, nope = h.dim - h.rot_part, nq = H * h.dim, nv = H * h.vdim, ldp = L.proj.N, ldkv = L.lat_ukv.N;
+      DENSE(e->pbuf, ldp, e->hx, d, L.proj, T, ACT_NONE);      // [dq | dkv] or [q | dkv | g] of the normed row
+      SegNormArgs sn;      // the latents' norms (fp32 statistics), written packed for the up-projections
+      sn.x = e->pbuf; sn.ldx = ldp; sn.T = T; sn.eps = s.eps; sn.elt = elt; sn.nseg = 0;
+      sn.col[sn.nseg] = L.lat_dkv; sn.n[sn.nseg] = h.kv_rank; sn.w[sn.nseg] = L.lat_kvnorm; sn.out[sn.nseg] = e->latc; sn.ldo[sn.nseg] = h.kv_rank; ++sn.nseg;
+      if (h.q_rank > 0) { sn.col[sn.nseg] = 0; sn.n[sn.nseg] = h.q_rank; sn.w[sn.nseg] = L.lat_qnorm; sn.out[sn.nseg] = e->latq; sn.ldo[sn.nseg] = h.q_rank; ++sn.nseg; }
+      HFWD(C_NORM, (double)T * (h.kv_rank + h.q_rank) * 2 * es, 0, segment_rmsnorm(sn, st));
+      void* q = e->pbuf; int ldq = ldp;
+      if (h.q_rank > 0) { DENSE(e->qbuf, nq, e->latq, h.q_rank, L.lat_uq, T, ACT_NONE); q = e->qbuf; ldq = nq; }
+      DENSE(e->latkv, ldkv, e->latc, h.kv_rank, L.lat_ukv, T, ACT_NONE);      // every head's unrotated key part, then its value
+      LatentKvArgs lk;
+      lk.q = q; lk.ldq = ldq; lk.k_nope = e->latkv; lk.ldk = ldkv; lk.v = at(e->latkv, (int64_t)H * nope); lk.ldv = ldkv;
+      lk.k_rot = at(e->pbuf, L.lat_dkv + h.kv_rank); lk.ldr = ldp; lk.freq = L.rot_freq; lk.rot_dims = h.rot_dims; lk.rot_part = h.rot_part;
+      lk.positions = m.pos; lk.slots = m.slots; lk.k_cache = L.kc; lk.v_cache = L.vc; lk.T = T; lk.H = H; lk.dim = h.dim; lk.vdim = h.vdim; lk.block_size = bs; lk.elt = elt;
+      HFWD(C_KVW, (double)T * (2.0 * H * h.rot_part + 2.0 * H * (h.dim + h.vdim)) * es, 0, latent_rotary_kvwrite(lk, st));
+      AttnBiasArgs aa;
+      aa.q = q; aa.ldq = ldq; aa.out = e->mixbuf; aa.ldo = nv; aa.k_cache = L.kc; aa.v_cache = L.vc;
+      aa.block_table = m.btab; aa.max_blocks = max_blocks; aa.seq_lens = m.seq_lens; aa.qsl = m.qsl; aa.positions = m.pos; aa.token_req = m.treq;
+      aa.B = B; aa.T = T; aa.H = H; aa.G = H; aa.dim = h.dim; aa.vdim = h.vdim; aa.block_size = bs; aa.chunk = 0;
+      aa.scale = h.scale; aa.bias_span = 0.f; aa.elt = elt;
+      for (int r = 0; r < B; ++r) aa.max_q = std::max(aa.max_q, hm.qsl[r + 1] - hm.qsl[r]);
+      while (aa.num_decode < B && hm.qsl[aa.num_decode + 1] - hm.qsl[aa.num_decode] == 1) ++aa.num_decode;
+      double keys = 0;
+      for (int t = 0; t < T; ++t) keys += hm.pos[t] + 1;
+      HFWD(decode_only ? C_ATT_DEC : C_ATT_GEN, (decode_only ? keys : (double)T) * H * (h.dim + h.vdim) * es + (double)T * H * (h.dim + h.vdim) * es,
+           2.0 * keys * H * (h.dim + h.vdim), attn_bias_chunk(aa, st));
+      if (h.out_gate) HFWD(C_ACT, (double)T * nv * 3 * es, 0, sigmoid_gate_mul(e->mixbuf, nv, at(e->pbuf, L.lat_g), ldp, T, nv, elt, st));
+      DENSE(e->obuf1, d, e->mixbuf, nv, L.o, T, ACT_NONE);
+      add_src(e->obuf1, d, 1.f);
     } else {
       const int ka = h.heads * h.vdim, ko = L.o2.K, ldp = L.proj.N;
       DENSE(e->pbuf, ldp, e->hx, d, L.proj, T, ACT_NONE);
@@ -512,26 +698,44 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
     }
     if (s.hyb_prenorm_pair && h.mlp != HybridLayerSpec::NONE) {
       // the feed-forward reads a norm of the stream that already holds the mixer's output
-      { const double nsrc = cb.n; HFWD(C_ACT, Td * (8 + nsrc * es), 0, flush()); }
-      HFWD(C_NORM, Td * (4 + es), 0, layer_norm(e->hx, nullptr, L.norm2, T, 1.f));
+      { const double nsrc = cb.n; HFWD(C_ACT, Td * (8.0 * S + nsrc * es), 0, flush()); }
+      sub = 1;
+      if (hyper) HFWD(C_NORM, Td * (4.0 * S + es), 0, stream_read(e->hx, L.hc_in[1], nullptr, L.norm2, T, 1.f, nullptr));
+      else HFWD(C_NORM, Td * (4 + es), 0, layer_norm(e->hx, nullptr, L.norm2, T, 1.f));
     }
-    if (h.mlp == HybridLayerSpec::DENSE) {
+    if (h.mlp == HybridLayerSpec::DENSE && h.ff_limit > 0.f) {
+      // clamped gated unit: bfloat16 forms the pair in the epilogue of the tensor-core GEMM over [gate | up]
+      const int f = h.ff;
+      const double gb = es * (2.0 * f * d + (double)T * (d + f)), gf = 4.0 * T * (double)f * d;
+      if (!e->f32 && f % 64 == 0 && d % 8 == 0) {
+        HFWD(T <= 256 ? C_GEMM_S : C_GEMM_L, gb, gf, kge_gemm_clamped_glu_bf16(e->ffbuf, e->hx, L.ff_gate, T, f, d, 1.702f, h.ff_limit, nullptr, 0, st));
+      } else {
+        LinearArgs sg;
+        sg.x = e->hx; sg.ldx = d; sg.w = L.ff_gate; sg.w2 = L.up.w; sg.y = e->ffbuf; sg.ldy = f; sg.T = T; sg.N = f; sg.K = d;
+        sg.glu = GLU_CLAMPED_SIGMOID; sg.glu_limit = h.ff_limit; sg.elt = elt; sg.out_f32 = e->f32;
+        HFWD(T <= 256 ? C_GEMM_S : C_GEMM_L, gb, gf, linear_any(sg, st));
+      }
+      DENSE(e->obuf2, d, e->ffbuf, f, L.down, T, ACT_NONE);
+      add_src(e->obuf2, d, 1.f);
+    } else if (h.mlp == HybridLayerSpec::DENSE) {
       DENSE(e->ffbuf, h.ff, e->hx, d, L.up, T, ACT_GELU_ERF);
       DENSE(e->obuf2, d, e->ffbuf, h.ff, L.down, T, ACT_NONE);
       add_src(e->obuf2, d, 1.f);
     } else if (h.mlp == HybridLayerSpec::MOE) {
       MoeRouteArgs ra;
       ra.h = e->hx; ra.ldh = d; ra.w_router = L.router.w; ra.b_router = L.router_b; ra.T = T; ra.d = d; ra.E = h.experts; ra.top = h.top;
-      const bool w_out = h.route == HybridLayerSpec::ROUTE_SOFTMAX_TOP;      // the routing weight multiplies the expert's output (in the fp32 sum below)
+      const bool w_out = h.route != HybridLayerSpec::ROUTE_SIGMOID_IN;      // the routing weight multiplies the expert's output (in the fp32 sum below)
       const bool clamped = h.glu == HybridLayerSpec::GLU_CLAMPED;
-      ra.score_fn = w_out ? 2 : 0; ra.renorm = false;
+      const bool ungated = h.glu == HybridLayerSpec::GLU_NONE_RELU2;      // one front matrix per expert, relu(.)^2
+      ra.score_fn = h.route == HybridLayerSpec::ROUTE_SOFTMAX_TOP ? 2 : h.route == HybridLayerSpec::ROUTE_SOFTMAX_ALL ? 1 : 0; ra.renorm = false;
+      ra.weight_scale = h.router_scale;
       if (L.s_sg) { ra.w_extra = L.s_sg; ra.extra_sigmoid = e->gates32; }      // the shared expert's per-token gate rides along, kept in fp32
       ra.group_off = e->moe_goff; ra.perm_token = e->moe_ptok; ra.perm_weight = e->moe_pw; ra.perm_dest = e->moe_pdest;
       ra.choice_expert = e->moe_cexp; ra.choice_weight = e->moe_cw; ra.elt = elt;
       const int np = T * h.top;
       // bfloat16 prompt steps with enough routed rows: groups padded to 256 rows for the grouped tensor-core GEMMs
       const int np_pad = (np / 256 + h.experts + 1) * 256;
-      const bool grouped = !e->f32 && !decode_only && np >= 512 && h.expert_ff % 64 == 0 && d % 8 == 0 && e->moe_xperm && np_pad <= e->moe_rows_padded;
+      const bool grouped = !ungated && !e->f32 && !decode_only && np >= 512 && h.expert_ff % 64 == 0 && d % 8 == 0 && e->moe_xperm && np_pad <= e->moe_rows_padded;
       if (grouped) { ra.pad = 256; ra.rows_padded = np_pad; ra.tile_group = e->moe_tile_group; }
       HFWD(C_MOE, Td * es + (double)h.experts * d * es, 2.0 * Td * h.experts, moe_route(ra, st));
       ++e->launches;
@@ -552,6 +756,7 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       g.x = e->hx; g.ldx = d; g.w = L.e_gate; g.w2 = L.e_up; g.y = e->moe_hidden; g.ldy = h.expert_ff; g.T = np; g.N = h.expert_ff; g.K = d;
       g.nz = h.experts; g.w_zs = (int64_t)2 * h.expert_ff * d; g.group_off = e->moe_goff; g.max_rows = np; g.xrows = e->moe_ptok; g.row_scale = w_out ? nullptr : e->moe_pw;
       if (clamped) { g.glu = GLU_CLAMPED_SIGMOID; g.glu_limit = h.expert_limit; }
+      if (ungated) { g.w2 = nullptr; g.w_zs = (int64_t)h.expert_ff * d; g.act = ACT_RELU2; }
       g.elt = elt; g.out_f32 = e->f32;
       HFWD(C_MOE, 2 * wexp + (double)np * (d + h.expert_ff) * es, 4.0 * np * (double)h.expert_ff * d, linear_any(g, st));
       LinearArgs dn;     // experts' down projection, scattered to row (token * top + choice)
@@ -579,14 +784,15 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       }
       // sum in a fixed order: mixer, the token's experts by choice, the shared expert
       for (int k = 0; k < h.top; ++k) {
-        if (cb.n == 4) HFWD(C_ACT, Td * (8 + 4 * es), 0, flush());
+        if (cb.n == 4) HFWD(C_ACT, Td * (8 + 4 * es), 0, flush_more());
         add_src(at(e->moe_out, (int64_t)k * d), h.top * d, 1.f, w_out ? e->moe_cw + k : nullptr, h.top);
       }
-      if (h.shared_ff > 0) { if (cb.n == 4) HFWD(C_ACT, Td * (8 + 4 * es), 0, flush()); add_src(e->obuf2, d, 1.f, L.s_sg ? e->gates32 : nullptr, 1); }
+      if (h.shared_ff > 0) { if (cb.n == 4) HFWD(C_ACT, Td * (8 + 4 * es), 0, flush_more()); add_src(e->obuf2, d, 1.f, L.s_sg ? e->gates32 : nullptr, 1); }
     }
-    { const double nsrc = cb.n; HFWD(C_ACT, Td * (8 + nsrc * es), 0, flush()); }
+    { const double nsrc = cb.n; HFWD(C_ACT, Td * (8.0 * S + nsrc * es), 0, flush()); }
     if (e->layer_dump_host && (int64_t)(i + 1) * T * d <= e->layer_dump_cap) {
-      KGE_CUDA_OK(cudaMemcpyAsync(e->layer_dump_host + (int64_t)i * T * d, e->res32, (size_t)T * d * 4, cudaMemcpyDeviceToHost, st));
+      if (hyper) { if (int rc = stream_read(nullptr, nullptr, nullptr, nullptr, T, 1.f, e->y32)) return rc; }      // the sum of the streams
+      KGE_CUDA_OK(cudaMemcpyAsync(e->layer_dump_host + (int64_t)i * T * d, hyper ? e->y32 : e->res32, (size_t)T * d * 4, cudaMemcpyDeviceToHost, st));
       KGE_CUDA_OK(cudaStreamSynchronize(st));
     }
   }
@@ -596,12 +802,14 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
     const double hb = es * ((double)s.vocab * d + (double)R * (d + s.vocab)), hf = 2.0 * R * (double)s.vocab * d;
     if (e->hyb_head_tc) {
       // norm (the logits' multiplier folded into it), then the tensor-core GEMM straight into the 16-bit logits
-      HFWD(C_NORM, (double)R * d * (4 + es), 0, layer_norm(e->hsel, m.rows, e->final_w, R, s.logit_scale));
+      if (hyper) HFWD(C_NORM, (double)R * d * (4.0 * S + es), 0, stream_read(e->hsel, nullptr, m.rows, e->final_w, R, s.logit_scale, nullptr));
+      else HFWD(C_NORM, (double)R * d * (4 + es), 0, layer_norm(e->hsel, m.rows, e->final_w, R, s.logit_scale));
       HFWD(R <= 256 ? C_GEMM_S : C_GEMM_L, hb, hf, kge_gemm_bf16(e->logits, e->hsel, e->lm_head, nullptr, R, s.vocab, d, 0, nullptr, 0, st));
       if (s.logit_softcap > 0.f) HFWD(C_SAMPLE, (double)R * s.vocab * (e->want_logits32 ? 8 : 4), 0, softcap_rows(e->want_logits32 ? e->logits32 : nullptr, e->logits, R, s.vocab, e->ld_logits, s.logit_softcap, st));
       else if (e->want_logits32) HFWD(C_SAMPLE, (double)R * s.vocab * 6, 0, elt16_to_f32(e->logits32, e->logits, (int64_t)R * s.vocab, st));
     } else {
-      HFWD(C_NORM, (double)R * d * (4 + es), 0, layer_norm(e->hsel, m.rows, e->final_w, R, 1.f));
+      if (hyper) HFWD(C_NORM, (double)R * d * (4.0 * S + es), 0, stream_read(e->hsel, nullptr, m.rows, e->final_w, R, 1.f, nullptr));
+      else HFWD(C_NORM, (double)R * d * (4 + es), 0, layer_norm(e->hsel, m.rows, e->final_w, R, 1.f));
       LinearArgs a;
       a.x = e->hsel; a.ldx = d; a.w = e->lm_head; a.y = e->logits32; a.ldy = s.vocab; a.T = R; a.N = s.vocab; a.K = d;
       a.alpha = s.logit_scale; a.elt = elt; a.out_f32 = true;

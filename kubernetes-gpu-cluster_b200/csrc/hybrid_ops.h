@@ -11,7 +11,7 @@
 namespace kge {
 
 enum { KGE_ELT_BF16 = 0, KGE_ELT_F32 = 1 };
-enum { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_SIGMOID = 4 };
+enum { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_SIGMOID = 4, ACT_TANH = 5, ACT_RELU2 = 6 };
 
 inline size_t elt_size(int elt) { return elt == KGE_ELT_F32 ? 4 : 2; }
 
@@ -156,14 +156,14 @@ int mlstm_step(const MlstmArgs& a, cudaStream_t st);
 inline int64_t mlstm_state_floats(int H, int dim, int vdim) { return (int64_t)H * ((int64_t)dim * vdim + dim + 1); }
 
 // Mixture-of-experts routing: logits z = W_router h (+ b_router) in fp32, scores sigmoid(z) (score_fn 0) or softmax(z) (1),
-// the `top` largest chosen (ties to the lower index), weights = scores, renormalised to sum 1 if renorm; score_fn 2:
+// the `top` largest chosen (ties to the lower index), weights = scores * weight_scale, renormalised to sum 1 first if renorm; score_fn 2:
 // the `top` largest LOGITS are chosen and the weights are the softmax over the chosen logits only.  Produces for every
 // expert the list of (token, choice) pairs routed to it: group_off [E + 1], perm_token [T * top] (the token row of
 // every permuted row), perm_weight [T * top], perm_dest [T * top] (row t * top + choice of the output buffer).
 struct MoeRouteArgs {
   const void* h = nullptr; int ldh = 0; const void* w_router = nullptr; const void* b_router = nullptr;
   const void* w_extra = nullptr; float* extra_sigmoid = nullptr;      // one more row [d]: extra_sigmoid[t] = sigmoid(w_extra . h_t) (a per-token gate)
-  int T = 0, d = 0, E = 0, top = 1, score_fn = 0; bool renorm = false;
+  int T = 0, d = 0, E = 0, top = 1, score_fn = 0; bool renorm = false; float weight_scale = 1.f;
   int32_t* group_off = nullptr; int32_t* perm_token = nullptr; float* perm_weight = nullptr; int32_t* perm_dest = nullptr;
   int32_t* choice_expert = nullptr; float* choice_weight = nullptr;     // scratch [T * top] each
   // pad > 1: every expert's rows start at a multiple of `pad` (group_off holds the padded offsets; perm_* have rows_padded
@@ -176,5 +176,74 @@ int moe_route(const MoeRouteArgs& a, cudaStream_t st);
 // routed rows made contiguous per expert: xperm[p, :] = bf16(perm_weight[p] * h[perm_token[p], :]) (null weights: 1); and back: out[perm_dest[p], :] = operm[p, :]
 int moe_gather_rows(void* xperm, const void* h, int ldh, const int32_t* perm_token, const float* perm_weight, int np, int d, cudaStream_t st);
 int moe_scatter_rows(void* out, const void* operm, const int32_t* perm_dest, int np, int d, cudaStream_t st);
+
+// Hyper-connected residual: S copies ("streams") of the fp32 residual stream, xs [T, S, d].
+//   embed_norm_streams: every stream of token t <- float(table[ids[t]]) (norm_w == null) or its RMS norm times norm_w
+//   stream_norm:        u = sum_s in_w[s] xs[row, s, :] (in_w null: plain sum);  y[r, :] = out_scale * u / sqrt(mean(u^2) + eps) * w
+//                       (row = rows ? rows[r] : r; y in elt); sum_out (fp32 [R, d], optional) receives u
+//   stream_combine:     with y[t, :] = y32[t, :] + sum_i scale_i * rscale_i(t) * src_i[t, :] (the sources of CombineArgs, summed
+//                       in order; y32 optional) and z = mult * col_scale[:] * y (col_scale null: 1), all streams at once from
+//                       the old ones: xs[t, j, :] <- sum_s mix[s * S + j] xs[t, s, :] + out_w[j] * z   (mix null: identity; out_w null: 1)
+// in_w / out_w / mix / col_scale are fp32 on the device.  S <= 8.
+int embed_norm_streams(float* xs, const int32_t* ids, const void* table, const void* norm_w, int T, int d, int S, float eps, int elt, cudaStream_t st);
+struct StreamNormArgs {
+  void* y = nullptr; const float* xs = nullptr; const float* in_w = nullptr; const int32_t* rows = nullptr; const void* w = nullptr;
+  float* sum_out = nullptr;
+  int R = 0, d = 0, S = 1; float eps = 1e-5f, out_scale = 1.f; int elt = KGE_ELT_BF16;
+};
+int stream_norm(const StreamNormArgs& a, cudaStream_t st);
+struct StreamCombineArgs {
+  float* xs = nullptr; CombineArgs src; const float* y32 = nullptr;
+  const float* col_scale = nullptr; const float* mix = nullptr; const float* out_w = nullptr;
+  float mult = 1.f; int T = 0, d = 0, S = 1; int elt = KGE_ELT_BF16;
+};
+int stream_combine(const StreamCombineArgs& a, cudaStream_t st);
+
+// WKV: a matrix-valued linear recurrence per head with a per-token, per-key-channel decay and a bonus for the current token.
+//   wkv_shift_mix: with h' the previous token's row of h (zeros at position 0; the slot's saved row where the step
+//     starts inside a sequence), mixes[z, t, :] = h + (h' - h) * mu[z, :] for z < nmix (mixes [nmix, T, d] in elt, mu
+//     [nmix, d] in elt); afterwards the slot keeps the last row of every request of the step (fp32).
+//   wkv_scan: per head, o_t = (S + diag(u) k_t v_t^T)^T r_t, then S <- diag(w_t) S + k_t v_t^T with
+//     w_t = exp(-exp(decay_pre_t)) (decay_pre fp32 [T, H * dim], the logit with its bias in); S [dim, dim] fp32 per slot and
+//     head, zero at position 0.  o is divided by its root mean square over the head (eps), multiplied by norm_w and by
+//     silu(gate_pre) and written to out [T, H * dim] (elt).  u fp32 [H * dim].  o32: fp32 scratch [T, H * dim].
+struct WkvArgs {
+  const void* h = nullptr; int ldh = 0; const void* mu = nullptr; void* mixes = nullptr; int nmix = 5; int d = 0;
+  const void* r = nullptr; const void* k = nullptr; const void* v = nullptr; const void* gate_pre = nullptr; int ld = 0;
+  const float* decay_pre = nullptr; const float* u = nullptr; const void* norm_w = nullptr;
+  float* o32 = nullptr; void* out = nullptr; int ldo = 0;
+  float* state = nullptr; int64_t slot_stride = 0;     // this layer's part of slot 0: [d] saved row, then [H, dim, dim]
+  const int32_t* slots = nullptr; const int32_t* qsl = nullptr; const int32_t* positions = nullptr; const int32_t* token_req = nullptr;
+  int B = 0, T = 0, H = 0, dim = 0;
+  float eps = 1e-5f;
+  int elt = KGE_ELT_BF16;
+};
+int wkv_shift_mix(const WkvArgs& a, cudaStream_t st);
+int wkv_scan(const WkvArgs& a, cudaStream_t st);
+inline int64_t wkv_state_floats(int d, int H, int dim) { return (int64_t)d + (int64_t)H * dim * dim; }
+
+// Attention through latents, the parts around the attention kernel.
+//   segment_rmsnorm: up to two column ranges of the rows of x (elt, row stride ldx) are RMS-normed in fp32 and written
+//     packed: out_i[t, :] = x[t, col_i : col_i + n_i] / sqrt(mean(.^2) + eps) * w_i.
+//   latent_rotary_kvwrite: q [T, H * dim] in place: the last rot_part dimensions of every head are the rotated part, of
+//     which the first rot_dims turn in interleaved pairs by position * freq[i] (angle in double precision); the shared
+//     key part k_rot [T, rot_part] turns the same way; head h's key cache row is [k_nope[t, h * (dim - rot_part) ...] | turned
+//     k_rot], its value cache row v[t, h * vdim ...].  Caches as in kv_write_any with G = H.
+//   sigmoid_gate_mul: y[t, c] <- y[t, c] * sigmoid(g[t, c]), c < n.
+struct SegNormArgs {
+  const void* x = nullptr; int ldx = 0; int T = 0; float eps = 1e-5f; int elt = KGE_ELT_BF16;
+  int nseg = 1; int col[2] = {0, 0}; int n[2] = {0, 0}; const void* w[2] = {nullptr, nullptr}; void* out[2] = {nullptr, nullptr}; int ldo[2] = {0, 0};
+};
+int segment_rmsnorm(const SegNormArgs& a, cudaStream_t st);
+struct LatentKvArgs {
+  void* q = nullptr; int ldq = 0; const void* k_nope = nullptr; int ldk = 0; const void* v = nullptr; int ldv = 0; const void* k_rot = nullptr; int ldr = 0;
+  const double* freq = nullptr; int rot_dims = 0, rot_part = 0;
+  const int32_t* positions = nullptr; const int64_t* slots = nullptr;
+  void* k_cache = nullptr; void* v_cache = nullptr;
+  int T = 0, H = 0, dim = 0, vdim = 0, block_size = 0;
+  int elt = KGE_ELT_BF16;
+};
+int latent_rotary_kvwrite(const LatentKvArgs& a, cudaStream_t st);
+int sigmoid_gate_mul(void* y, int ldy, const void* g, int ldg, int T, int n, int elt, cudaStream_t st);
 
 }  // namespace kge

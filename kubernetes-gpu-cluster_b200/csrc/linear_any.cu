@@ -21,6 +21,8 @@ __device__ __forceinline__ float act_apply(int act, float v) {
     case ACT_GELU_TANH: return 0.5f * v * (1.f + tanhf(0.79788456080286536f * (v + 0.044715f * v * v * v)));
     case ACT_SILU: return v / (1.f + expf(-v));
     case ACT_SIGMOID: return 1.f / (1.f + expf(-v));
+    case ACT_TANH: return tanhf(v);
+    case ACT_RELU2: { const float r = fmaxf(v, 0.f); return r * r; }
     default: return v;
   }
 }

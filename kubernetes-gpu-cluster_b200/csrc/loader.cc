@@ -36,7 +36,7 @@ static bool parse_hybrid_mlp(const Json& l, HybridLayerSpec* hp, std::string* er
   const Json* f = l.get("mlp");
   if (f && f->is_obj()) {
     const std::string kind = f->str_or("kind", "");
-    if (kind == "dense") { h.mlp = HybridLayerSpec::DENSE; h.ff = (int)f->int_or("ff", 0); if (h.ff <= 0) { *err = "config.json: dense mlp without ff"; return false; } }
+    if (kind == "dense") { h.mlp = HybridLayerSpec::DENSE; h.ff = (int)f->int_or("ff", 0); h.ff_limit = (float)f->num_or("limit", 0.0); if (h.ff <= 0) { *err = "config.json: dense mlp without ff"; return false; } }
     else if (kind == "moe") {
       h.mlp = HybridLayerSpec::MOE;
       const Json *ex = f->get("expert"), *ro = f->get("router"), *sh = f->get("shared");
@@ -44,6 +44,7 @@ static bool parse_hybrid_mlp(const Json& l, HybridLayerSpec* hp, std::string* er
       h.expert_ff = (int)ex->int_or("ff", 0); h.experts = (int)ro->int_or("experts", 0); h.top = (int)ro->int_or("top", 1);
       if (sh && sh->is_obj()) { h.shared_ff = (int)sh->int_or("ff", 0); h.shared_limit = (float)sh->num_or("limit", 0.0); }
       h.expert_limit = (float)ex->num_or("limit", 0.0);
+      h.router_scale = (float)ro->num_or("scale", 1.0);
       if (h.expert_ff <= 0 || h.experts <= 0 || h.top <= 0 || h.top > h.experts) { *err = "config.json: bad moe sizes"; return false; }
     } else { *err = "config.json: unknown mlp kind '" + kind + "'"; return false; }
   }
@@ -158,9 +159,94 @@ static bool parse_girolorn(const Json& j, ModelSpec* s, std::string* err) {
   return true;
 }
 
+// Zezilix: a layer list of WKV recurrences and latent attention (two kinds: queries through a normed latent, or
+// queries from one matrix with a sigmoid output gate), dense clamped gated units or softmax-routed mixtures of ungated
+// squared-ReLU experts, on a hyper-connected residual (several streams, per-sublayer read / mix / write weights) with
+// a multiplier and a per-layer scale vector on every sublayer's result; the embedding is normed; a run of layers may
+// repeat with the same tensors (every pass with a cache and state of its own), which the list below holds unrolled.
+static bool parse_zezilix(const Json& j, ModelSpec* s, std::string* err) {
+  s->model_type = "zezilix";
+  s->vocab = (int)j.int_or("vocab", 0);
+  s->d = (int)j.int_or("width", 0);
+  if (const Json* n = j.get("norm")) s->eps = (float)n->num_or("eps", 1e-5);
+  s->hyb_prenorm_pair = true;
+  s->embed_norm = true;
+  s->streams = (int)j.int_or("streams", 1);
+  s->residual_mult = (float)j.num_or("residual_mult", 1.0);
+  s->max_pos = 1 << 20;                 // rotary angles are computed from the position: no table bounds them
+  s->torch_dtype = "bfloat16";
+  s->bos = (int)j.int_or("bos_token_id", -1);
+  s->eos = (int)j.int_or("eos_token_id", -1);
+  if (s->streams < 1 || s->streams > 8) { *err = "config.json: 'streams' must be 1 .. 8"; return false; }
+  const Json* ls = j.get("layers");
+  if (!ls || !ls->is_arr() || ls->arr.empty()) { *err = "config.json: 'layers' must be a non-empty array"; return false; }
+  std::vector<HybridLayerSpec> own;
+  for (const Json& l : ls->arr) {
+    HybridLayerSpec h;
+    const std::string type = l.str_or("type", "");
+    const Json* m = l.get("mixer");
+    if (!m || !m->is_obj()) { *err = "config.json: a layer has no 'mixer'"; return false; }
+    h.heads = (int)m->int_or("heads", 0);
+    const int dim = (int)m->int_or("dim", 0);
+    if (type == "wkv") {
+      h.mixer = HybridLayerSpec::WKV;
+      h.dim = h.vdim = dim; h.kv_heads = h.heads;
+      h.decay_rank = (int)m->int_or("decay_rank", 0);
+      if (h.heads <= 0 || dim <= 0 || h.decay_rank < 0) { *err = "config.json: bad wkv sizes"; return false; }
+    } else if (type == "latent_attention" || type == "latent_attention_2") {
+      h.mixer = HybridLayerSpec::LATENT;
+      h.out_gate = type == "latent_attention_2";
+      h.kv_heads = h.heads;
+      h.rot_part = (int)m->int_or("rot_dim", 0);
+      h.dim = dim + h.rot_part;
+      h.vdim = (int)m->int_or("vdim", dim);
+      h.kv_rank = (int)m->int_or("kv_rank", 0);
+      h.q_rank = (int)m->int_or("q_rank", 0);
+      h.scale = (float)m->num_or("scale", 1.0);
+      h.rot_dims = h.rot_part;
+      if (const Json* r = m->get("rot")) if (r->is_obj()) { h.rot_dims = (int)r->int_or("dims", h.rot_part); h.rot_base = r->num_or("base", 10000.0); }
+      if (h.heads <= 0 || dim < 0 || h.dim <= 0 || h.vdim <= 0 || h.kv_rank <= 0 || h.q_rank < 0 || h.rot_part < 0 || h.rot_dims < 0 || h.rot_dims > h.rot_part ||
+          h.rot_dims % 2 || h.rot_base <= 0.0) { *err = "config.json: bad latent-attention sizes"; return false; }
+      if (h.out_gate && h.q_rank > 0) { *err = "config.json: 'latent_attention_2' has no query latent"; return false; }
+      if (!h.out_gate && h.q_rank <= 0) { *err = "config.json: 'latent_attention' needs 'q_rank'"; return false; }
+    } else { *err = "config.json: unknown layer type '" + type + "' (wkv, latent_attention, latent_attention_2)"; return false; }
+    if (!parse_hybrid_mlp(l, &h, err)) return false;
+    if (h.mlp == HybridLayerSpec::DENSE && h.ff_limit <= 0.f) { *err = "config.json: a dense mlp needs a positive 'limit'"; return false; }
+    if (h.mlp == HybridLayerSpec::MOE) {
+      if (h.shared_ff > 0) { *err = "config.json: this architecture has no shared expert"; return false; }
+      h.route = HybridLayerSpec::ROUTE_SOFTMAX_ALL; h.glu = HybridLayerSpec::GLU_NONE_RELU2;
+    }
+    own.push_back(h);
+  }
+  // run order: layers before the loop, the looped run `times` times, the rest
+  const int n = (int)own.size();
+  int start = 0, stop = 0, times = 1;
+  if (const Json* lp = j.get("loop")) {
+    if (lp->is_obj()) {
+      start = (int)lp->int_or("start", 0); stop = (int)lp->int_or("stop", start); times = (int)lp->int_or("times", 1);
+      if (start < 0 || stop < start || stop > n || times < 1) { *err = "config.json: bad 'loop'"; return false; }
+    }
+  }
+  std::vector<int> first_run((size_t)n, -1);
+  auto push = [&](int i) {
+    HybridLayerSpec h = own[(size_t)i];
+    h.tensor_index = i;
+    if (first_run[(size_t)i] >= 0) h.weights_of = first_run[(size_t)i];
+    else first_run[(size_t)i] = (int)s->hybrid.size();
+    s->hybrid.push_back(h);
+  };
+  for (int i = 0; i < start; ++i) push(i);
+  for (int t = 0; t < times; ++t) for (int i = start; i < stop; ++i) push(i);
+  for (int i = stop; i < n; ++i) push(i);
+  s->L = (int)s->hybrid.size();
+  if (s->vocab <= 0 || s->d <= 0) { *err = "config.json misses a required size"; return false; }
+  return true;
+}
+
 static bool parse_config(const Json& j, ModelSpec* s, std::string* err) {
   if (j.str_or("architecture", "") == "Safupel") return parse_hybrid(j, s, err);
   if (j.str_or("architecture", "") == "Girolorn") return parse_girolorn(j, s, err);
+  if (j.str_or("architecture", "") == "Zezilix") return parse_zezilix(j, s, err);
   s->model_type = j.str_or("model_type", "");
   s->vocab = (int)j.int_or("vocab_size", 0);
   s->d = (int)j.int_or("hidden_size", 0);
@@ -387,7 +473,7 @@ extern "C" int kge_model_spec_json(const kge_model_dir* m, char* out, int cap) {
   if (s.is_hybrid()) {
     std::string j = "{\"model_type\":\"" + s.model_type + "\",\"vocab\":" + std::to_string(s.vocab) + ",\"d\":" + std::to_string(s.d) +
                     ",\"L\":" + std::to_string(s.L) + ",\"has_weights\":" + (m->md.has_weights() ? "true" : "false") + ",\"layers\":[";
-    char buf[1024];
+    char buf[2048];
     for (size_t i = 0; i < s.hybrid.size(); ++i) {
       const kge::HybridLayerSpec& h = s.hybrid[i];
       snprintf(buf, sizeof buf,
@@ -395,14 +481,17 @@ extern "C" int kge_model_spec_json(const kge_model_dir* m, char* out, int cap) {
                "\"scale\":%.9g,\"left_scale\":%.9g,\"right_scale\":%.9g,\"m_heads\":%d,\"m_dim\":%d,\"m_vdim\":%d,\"gate_cap\":%.9g,"
                "\"mlp\":%d,\"ff\":%d,\"experts\":%d,\"top\":%d,\"expert_ff\":%d,\"shared_ff\":%d,\"softcap\":%.9g,\"rot_dims\":%d,\"rot_base\":%.17g,"
                "\"yarn_factor\":%.17g,\"yarn_original\":%.17g,\"yarn_fast\":%.17g,\"yarn_slow\":%.17g,\"route\":%d,\"glu\":%d,\"expert_limit\":%.9g,"
-               "\"shared_limit\":%.9g,\"weights_of\":%d}",
+               "\"shared_limit\":%.9g,\"weights_of\":%d,\"tensor_index\":%d,\"q_rank\":%d,\"kv_rank\":%d,\"rot_part\":%d,\"out_gate\":%d,"
+               "\"decay_rank\":%d,\"ff_limit\":%.9g,\"router_scale\":%.9g}",
                i ? "," : "", h.mixer, h.width, h.blocks, h.conv, h.heads, h.kv_heads, h.dim, h.vdim, h.chunk, (double)h.scale, (double)h.left_scale,
                (double)h.right_scale, h.m_heads, h.m_dim, h.m_vdim, (double)h.gate_cap, h.mlp, h.ff, h.experts, h.top, h.expert_ff, h.shared_ff,
                (double)h.softcap, h.rot_dims, h.rot_base, h.yarn_factor, h.yarn_original, h.yarn_fast, h.yarn_slow, h.route, h.glu, (double)h.expert_limit,
-               (double)h.shared_limit, h.weights_of);
+               (double)h.shared_limit, h.weights_of, h.tensor_index < 0 ? (int)i : h.tensor_index, h.q_rank, h.kv_rank, h.rot_part, h.out_gate ? 1 : 0,
+               h.decay_rank, (double)h.ff_limit, (double)h.router_scale);
       j += buf;
     }
-    snprintf(buf, sizeof buf, "],\"eps\":%.9g,\"logit_scale\":%.9g,\"logit_softcap\":%.9g}", (double)s.eps, (double)s.logit_scale, (double)s.logit_softcap);
+    snprintf(buf, sizeof buf, "],\"eps\":%.9g,\"logit_scale\":%.9g,\"logit_softcap\":%.9g,\"streams\":%d,\"residual_mult\":%.9g,\"embed_norm\":%s}", (double)s.eps,
+             (double)s.logit_scale, (double)s.logit_softcap, s.streams, (double)s.residual_mult, s.embed_norm ? "true" : "false");
     j += buf;
     KGE_REQUIRE((int)j.size() < cap, "kge_model_spec_json: buffer of %d bytes too small", cap);
     memcpy(out, j.c_str(), j.size() + 1);

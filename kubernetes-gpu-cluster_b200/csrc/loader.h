@@ -12,7 +12,7 @@ namespace kge {
 // One layer of a layer-list ("hybrid") model: which token mixer it has, that mixer's sizes and constants, and its
 // feed-forward.  Every number comes from config.json; the kernels take them as parameters.
 struct HybridLayerSpec {
-  enum Mixer { RGLRU = 0, PARALLEL = 1, ATTENTION = 2 };
+  enum Mixer { RGLRU = 0, PARALLEL = 1, ATTENTION = 2, WKV = 3, LATENT = 4 };
   enum Mlp { NONE = 0, DENSE = 1, MOE = 2 };
   int mixer = RGLRU;
   // gated linear recurrence (RG-LRU): two branches of `width`, gates block-diagonal in `blocks` parts, causal conv of `conv` taps
@@ -33,27 +33,45 @@ struct HybridLayerSpec {
   bool sink = false, qk_norm = false, v_from_k = false;
   int rot_dims = 0;
   double rot_base = 10000.0, yarn_factor = 0.0, yarn_original = 0.0, yarn_fast = 32.0, yarn_slow = 1.0;
+  // matrix-valued linear recurrence with a per-channel, per-token decay (WKV): `heads` x (`dim` x `dim`) state, every
+  // projection reads its own blend of the token and the one before it, the decay's logit comes through a low-rank pair
+  // of `decay_rank` columns (taken from the checkpoint's shapes when 0)
+  int decay_rank = 0;
+  // attention through latents (LATENT): keys and values are up-projections of one normed latent of `kv_rank` numbers per
+  // token; a key is [dim - rot_part unrotated | rot_part rotated] where the rotated part comes straight from the
+  // down-projection and is shared by all heads; queries come through a normed latent of `q_rank` numbers (0: one
+  // matrix); rotary positions act on the first rot_dims of the rot_part; out_gate: the heads' outputs are multiplied by
+  // sigmoid(W_g h) before the output matrix.  heads = kv_heads, dim counts the whole key, vdim the value.
+  int q_rank = 0, kv_rank = 0, rot_part = 0;
+  bool out_gate = false;
   // feed-forward
   int mlp = NONE;
   int ff = 0;                                    // dense
+  float ff_limit = 0.f;                          // dense: > 0 - a clamped gated unit (gate, up, down) with this limit; 0 - up, GELU, down
   int experts = 0, top = 0, expert_ff = 0, shared_ff = 0;   // mixture of experts (+ an always-on shared expert if shared_ff > 0)
   // how the experts are chosen and weighed: ROUTE_SIGMOID_IN - sigmoid scores, the weight multiplies the expert's input;
   // ROUTE_SOFTMAX_TOP - the largest logits (router bias added), softmax over the chosen logits only, the weight multiplies
   // the expert's output
-  enum Route { ROUTE_SIGMOID_IN = 0, ROUTE_SOFTMAX_TOP = 1 };
+  // ROUTE_SOFTMAX_ALL - softmax over all experts, the largest scores chosen, weight = score * router_scale (not
+  // renormalised), multiplies the expert's output
+  enum Route { ROUTE_SIGMOID_IN = 0, ROUTE_SOFTMAX_TOP = 1, ROUTE_SOFTMAX_ALL = 2 };
   int route = ROUTE_SIGMOID_IN;
+  float router_scale = 1.f;
   bool router_bias = false;
   // the experts' gated unit: GLU_SILU - silu(gate) * up; GLU_CLAMPED - g = min(gate, limit), u = clamp(up, -limit, limit),
   // g * sigmoid(1.702 g) * (u + 1)
-  enum Glu { GLU_SILU = 0, GLU_CLAMPED = 1 };
+  // GLU_NONE_RELU2 - no gate: down(relu(up h)^2)
+  enum Glu { GLU_SILU = 0, GLU_CLAMPED = 1, GLU_NONE_RELU2 = 2 };
   int glu = GLU_SILU;
   float expert_limit = 0.f, shared_limit = 0.f;
   bool shared_gate = false;                      // the shared expert's output is multiplied by sigmoid(w_sg . h), one number per token
   int weights_of = -1;                           // >= 0: this layer owns no tensors and runs with that layer's (cache and state stay its own)
+  int tensor_index = -1;                         // the 'l<i>.' prefix of this layer's tensors (-1: its place in the list)
+  bool has_cache() const { return mixer == PARALLEL || mixer == ATTENTION || mixer == LATENT; }
 };
 
 struct ModelSpec {
-  std::string model_type;       // "opt" | "llama" | "qwen2" | "qwen3" | "safupel" | "girolorn"
+  std::string model_type;       // "opt" | "llama" | "qwen2" | "qwen3" | "safupel" | "girolorn" | "zezilix"
   // layer-list models (config.json "architecture"): per-layer descriptions and the multiplier of the logits
   std::vector<HybridLayerSpec> hybrid;
   float logit_scale = 1.f;
@@ -62,6 +80,13 @@ struct ModelSpec {
   // (hyb_prenorm_pair) a norm before the mixer and, after the mixer's sum, another before the feed-forward;
   // hyb_layernorm: mean-centred layer norm with a weight and no bias instead of the RMS norm
   bool hyb_prenorm_pair = false, hyb_layernorm = false;
+  // hyper-connected residual: `streams` >= 1 copies of the residual stream, read through per-sublayer input weights,
+  // mixed by a streams x streams matrix and written through output weights (0: one plain residual stream); every
+  // sublayer's result is multiplied by residual_mult and, element by element, by a per-layer scale vector; the
+  // embedding goes through the model's norm before the first layer
+  int streams = 0;
+  float residual_mult = 1.f;
+  bool embed_norm = false;
   bool is_hybrid() const { return !hybrid.empty(); }
   bool qkv_bias = false;        // qwen2: q/k/v projections carry a bias
   bool qk_norm = false;         // qwen3: RMSNorm over head_dim on q and k, per head, before RoPE

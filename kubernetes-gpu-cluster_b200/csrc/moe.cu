@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(256) moe_score_kernel(MoeRouteArgs a) {
       for (int k = 0; k < a.top; ++k) total += cw[k];
       for (int k = 0; k < a.top; ++k) cw[k] /= total;
     }
+    if (a.weight_scale != 1.f) for (int k = 0; k < a.top; ++k) cw[k] *= a.weight_scale;
   }
 }
 

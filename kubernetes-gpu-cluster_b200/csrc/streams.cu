@@ -1,0 +1,128 @@
+// Hyper-connected residual for layer-list models: the residual stream exists in S copies ("streams"), xs [T, S, d] in
+// fp32.  A sublayer reads a weighted sum of the streams through an RMS norm, and its result y comes back into every
+// stream while the old streams are mixed by an S x S matrix:
+//     u = sum_s in[s] x_s,    x_j <- sum_s mix[s, j] x_s + out[j] * (mult * col_scale . y)
+// With S = 1, in = out = mix = 1 this is the plain pre-norm residual x <- x + mult * col_scale . y.  One block per
+// token; every sum of a row runs in a fixed order in fp32, whatever else the launch holds.
+#include "common.cuh"
+#include "elt_access.cuh"
+#include "hybrid_ops.h"
+
+namespace kge {
+
+constexpr int SMAX = 8;
+
+template <typename E>
+__global__ void __launch_bounds__(256) embed_norm_streams_kernel(float* xs, const int32_t* ids, const E* table, const E* norm_w, int d, int S, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const E* row = table + (int64_t)ids[t] * d;
+  float inv = 1.f;
+  if (norm_w) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) { const float v = ldf(row + c); ss = fmaf(v, v, ss); }
+    inv = 1.f / sqrtf(block_sum(ss, red) / (float)d + eps);
+  }
+  float* x = xs + (int64_t)t * S * d;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float v = norm_w ? ldf(row + c) * inv * ldf(norm_w + c) : ldf(row + c);
+    for (int s = 0; s < S; ++s) x[(int64_t)s * d + c] = v;
+  }
+}
+
+int embed_norm_streams(float* xs, const int32_t* ids, const void* table, const void* norm_w, int T, int d, int S, float eps, int elt, cudaStream_t st) {
+  if (T <= 0) return 0;
+  KGE_REQUIRE(S >= 1 && S <= SMAX, "embed_norm_streams: %d streams", S);
+  cudaError_t ce = elt == KGE_ELT_F32
+      ? launch_pdl(embed_norm_streams_kernel<float>, dim3(T), dim3(256), 0, st, xs, ids, (const float*)table, (const float*)norm_w, d, S, eps)
+      : launch_pdl(embed_norm_streams_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, st, xs, ids, (const __nv_bfloat16*)table, (const __nv_bfloat16*)norm_w, d, S, eps);
+  KGE_CUDA_OK(ce);
+  return 0;
+}
+
+// u is kept in shared memory between the sum of squares and the write (one read of the streams)
+template <typename E>
+__global__ void __launch_bounds__(256) stream_norm_kernel(StreamNormArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float u[];
+  __shared__ float red[33];
+  __shared__ float win[SMAX];
+  const int r = blockIdx.x, row = a.rows ? a.rows[r] : r, d = a.d, S = a.S;
+  if (threadIdx.x < S) win[threadIdx.x] = a.in_w ? a.in_w[threadIdx.x] : 1.f;
+  __syncthreads();
+  const float* x = a.xs + (int64_t)row * S * d;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float v = win[0] * x[c];
+    for (int s = 1; s < S; ++s) v = fmaf(win[s], x[(int64_t)s * d + c], v);
+    u[c] = v;
+    ss = fmaf(v, v, ss);
+  }
+  const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)d + a.eps) * a.out_scale;
+  E* y = (E*)a.y + (int64_t)r * d;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float v = u[c];
+    if (a.y) stf(y + c, v * inv * ldf((const E*)a.w + c));
+    if (a.sum_out) a.sum_out[(int64_t)r * d + c] = v;
+  }
+}
+
+int stream_norm(const StreamNormArgs& a, cudaStream_t st) {
+  if (a.R <= 0) return 0;
+  KGE_REQUIRE(a.S >= 1 && a.S <= SMAX && a.d > 0 && (size_t)a.d * 4 <= 200 * 1024, "stream_norm: %d streams of %d columns", a.S, a.d);
+  const size_t smem = (size_t)a.d * 4;
+  static size_t smem_set = 0;
+  if (smem > 48 * 1024 && smem > smem_set) {
+    KGE_CUDA_OK(cudaFuncSetAttribute(stream_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    KGE_CUDA_OK(cudaFuncSetAttribute(stream_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    smem_set = smem;
+  }
+  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(stream_norm_kernel<float>, dim3(a.R), dim3(256), smem, st, a)
+                                        : launch_pdl(stream_norm_kernel<__nv_bfloat16>, dim3(a.R), dim3(256), smem, st, a);
+  KGE_CUDA_OK(ce);
+  return 0;
+}
+
+template <typename E>
+__global__ void __launch_bounds__(256) stream_combine_kernel(StreamCombineArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float mix[SMAX * SMAX], wout[SMAX], rs[4];
+  const int t = blockIdx.x, d = a.d, S = a.S;
+  if (threadIdx.x < S * S) mix[threadIdx.x] = a.mix ? a.mix[threadIdx.x] : (threadIdx.x / S == threadIdx.x % S ? 1.f : 0.f);
+  if (threadIdx.x < S) wout[threadIdx.x] = a.out_w ? a.out_w[threadIdx.x] : 1.f;
+  if (threadIdx.x < a.src.n) rs[threadIdx.x] = a.src.scale[threadIdx.x] * (a.src.rscale[threadIdx.x] ? a.src.rscale[threadIdx.x][(int64_t)t * a.src.rs_stride[threadIdx.x]] : 1.f);
+  __syncthreads();
+  float* x = a.xs + (int64_t)t * S * d;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float y = a.y32 ? a.y32[(int64_t)t * d + c] : 0.f;
+    for (int i = 0; i < a.src.n; ++i) y = fmaf(rs[i], ldf((const E*)a.src.src[i] + (int64_t)t * a.src.ld[i] + c), y);
+    const float z = a.mult * (a.col_scale ? a.col_scale[c] : 1.f) * y;
+    float old[SMAX];
+#pragma unroll
+    for (int s = 0; s < SMAX; ++s) old[s] = s < S ? x[(int64_t)s * d + c] : 0.f;
+#pragma unroll
+    for (int j = 0; j < SMAX; ++j) {
+      if (j < S) {
+        float v = 0.f;
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s) if (s < S) v = fmaf(mix[s * S + j], old[s], v);
+        x[(int64_t)j * d + c] = fmaf(wout[j], z, v);
+      }
+    }
+  }
+}
+
+int stream_combine(const StreamCombineArgs& a, cudaStream_t st) {
+  if (a.T <= 0) return 0;
+  KGE_REQUIRE(a.S >= 1 && a.S <= SMAX && a.src.n >= 0 && a.src.n <= 4, "stream_combine: %d streams, %d sources", a.S, a.src.n);
+  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(stream_combine_kernel<float>, dim3(a.T), dim3(256), 0, st, a)
+                                        : launch_pdl(stream_combine_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), 0, st, a);
+  KGE_CUDA_OK(ce);
+  return 0;
+}
+
+}  // namespace kge
