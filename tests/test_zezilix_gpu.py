@@ -196,7 +196,7 @@ def test_mixed_batches_of_unequal_requests(kge, tmp_path, dtype):
     llm.close()
     for r in P:
         assert at[r] == len(P[r])
-        check(np.concatenate(got[r]), want[r][0], dtype, f"request {r}", want[r][1], oz.bfloat16_noise(cfg, W, P[0]))
+        check(np.concatenate(got[r]), want[r][0], dtype, f"request {r}", want[r][1], oz.bfloat16_noise(cfg, W, P[r]))
 
 
 def test_pages_and_slots_are_used_again(kge, tmp_path):
