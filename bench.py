@@ -2,7 +2,7 @@
 """Headline benchmark: output tokens/s at fixed concurrency (BASELINE.json `metric`).
 
   python bench.py --gpus N --steps K --warmup W [--workload c3|c2|c1] [--impl ours|reference]
-  python bench.py --designs [safupel|girolorn]   (a layer-list design beside a Llama of equal size; one JSON line per size)
+  python bench.py --designs [safupel|girolorn|zezilix]   (a layer-list design beside the closest other model of equal size; one JSON line per size)
 
 A "step" is one whole job of the workload: every request prefilled (2k-token prompts, 8192 tokens
 per engine step as the continuous-batching scheduler cuts them) and decoded greedily to its output length.
@@ -569,6 +569,34 @@ def girolorn_configs(z):
     return gir, lla
 
 
+ZEZILIX_SIZES = {
+    # WKV recurrences and latent attention with squared-ReLU experts (Zezilix) at sizes that resemble real layers: keys of
+    # 64 unrotated + 64 rotated numbers, values of 128, latents of 512 (keys / values) and 768 (queries); the model beside it
+    # is the closest one the engine has, the attention + mixture-of-experts design (Girolorn) of the same width, depth,
+    # heads and experts
+    "w2048": dict(width=2048, vocab=32000, heads=16, dim=64, rot=64, vdim=128, kv_rank=512, q_rank=768, wkv_heads=32, wkv_dim=64, decay_rank=64, ff=8192,
+                  experts=16, top=2, eff=1024, loop=(1, 3, 2), tail=True, girolorn="w2048"),
+    "w4096": dict(width=4096, vocab=32000, heads=32, dim=64, rot=64, vdim=128, kv_rank=512, q_rank=1536, wkv_heads=64, wkv_dim=64, decay_rank=64, ff=14336,
+                  experts=8, top=2, eff=3584, loop=(1, 3, 1), tail=False, girolorn="w4096"),
+}
+
+
+def zezilix_configs(z):
+    rot = {"base": 1000000.0, "dims": z["rot"]}
+    lat = {"dim": z["dim"], "heads": z["heads"], "kv_rank": z["kv_rank"], "rot": rot, "rot_dim": z["rot"], "scale": (z["dim"] + z["rot"]) ** -0.5, "vdim": z["vdim"]}
+    wkv = {"dim": z["wkv_dim"], "heads": z["wkv_heads"], "decay_rank": z["decay_rank"]}
+    moe = {"expert": {"ff": z["eff"]}, "kind": "moe", "router": {"experts": z["experts"], "scale": 2.5, "top": z["top"]}}
+    layers = [{"mixer": wkv, "mlp": {"ff": z["ff"], "kind": "dense", "limit": 7.0}, "type": "wkv"},
+              {"mixer": lat, "mlp": moe, "type": "latent_attention_2"},
+              {"mixer": dict(lat, q_rank=z["q_rank"]), "mlp": moe, "type": "latent_attention"},
+              {"mixer": wkv, "mlp": moe, "type": "wkv"}]
+    if z["tail"]:
+        layers += [{"mixer": lat, "mlp": moe, "type": "latent_attention_2"}, {"mixer": dict(lat, q_rank=z["q_rank"]), "mlp": moe, "type": "latent_attention"}]
+    zez = {"architecture": "Zezilix", "layers": layers, "loop": dict(zip(("start", "stop", "times"), z["loop"])), "norm": {"eps": 1e-6}, "residual_mult": 0.3,
+           "streams": 2, "vocab": z["vocab"], "width": z["width"]}
+    return zez, girolorn_configs(GIROLORN_SIZES[z["girolorn"]])[0]
+
+
 def time_raw_steps(kge, llm, batch_np, steps, warmup):
     """Wall-clock seconds per synchronous engine step (metadata upload, kernels, sampled ids back), after warm-up."""
     import ctypes as C
@@ -600,7 +628,7 @@ def raw_batch(B, ctx, q, bs, vocab, seed):
 
 
 def run_designs(args):
-    """--designs [safupel|girolorn]: a layer-list design next to a Llama of equal size (random weights): one prefill step of 4 x 2048 tokens,
+    """--designs [safupel|girolorn|zezilix]: a layer-list design next to a Llama (or the closest other design) of equal size (random weights): one prefill step of 4 x 2048 tokens,
     one decode step of 64 requests at context 2048, wall-clock per step plus per-kernel device times against the roofline."""
     from kge_loader import load
     kge = load()
@@ -608,7 +636,10 @@ def run_designs(args):
     hbm, tf, src = peaks()
     B, ctx, PB, bs = 64, 2048, 4, args.block_size
     which = args.designs
-    sizes, make, arms = (GIROLORN_SIZES, girolorn_configs, ("girolorn", "llama")) if which == "girolorn" else (DESIGN_SIZES, design_configs, ("safupel", "llama"))
+    sizes, make, arms = {"girolorn": (GIROLORN_SIZES, girolorn_configs, ("girolorn", "llama")), "zezilix": (ZEZILIX_SIZES, zezilix_configs, ("zezilix", "girolorn")),
+                         "safupel": (DESIGN_SIZES, design_configs, ("safupel", "llama"))}[which]
+    if args.sizes:
+        sizes = {k: v for k, v in sizes.items() if k in args.sizes.split(",")}
     for name, z in sizes.items():
         line = {"design_compare": name, "design": which, "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
                 "prefill": f"{PB} x {ctx} tokens in one step", "decode": f"{B} requests, one token each at context {ctx}", "arms": {}}
@@ -672,7 +703,8 @@ def main():
     ap.add_argument("--no-tp", action="store_true", help="at N > 1, skip the tensor-parallel (config 4) sub-record")
     ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"], help="TP data path: peer memory (default) or NCCL")
     ap.add_argument("--tp-timeout", type=float, default=420.0, help="seconds the tensor-parallel leg may take at N > 1")
-    ap.add_argument("--designs", nargs="?", const="safupel", default=None, choices=["safupel", "girolorn"],
+    ap.add_argument("--sizes", default="", help="with --designs: the sizes to run, with commas between them (all by default)")
+    ap.add_argument("--designs", nargs="?", const="safupel", default=None, choices=["safupel", "girolorn", "zezilix"],
                     help="instead of the workload: a layer-list design (safupel, the default, or girolorn) beside a Llama of equal "
                     "size, prefill and decode steps with per-kernel rooflines (one GPU, random weights)")
     args = ap.parse_args()

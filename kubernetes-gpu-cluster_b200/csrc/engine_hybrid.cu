@@ -382,7 +382,7 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
     // split-KV scratch of the TMA-staged decode attention, for attention mixers whose heads it takes
     int64_t need = 0;
     for (auto& h : s.hybrid)
-      if (h.mixer == HybridLayerSpec::ATTENTION && !e->f32 && (h.dim == 64 || h.dim == 128) && h.vdim == h.dim)
+      if ((h.mixer == HybridLayerSpec::ATTENTION || h.mixer == HybridLayerSpec::LATENT) && !e->f32 && (h.dim == 64 || h.dim == 128) && h.vdim == h.dim)
         need = std::max<int64_t>(need, kge_attn_workspace_bytes(Rm, h.heads, h.dim, e->cfg.max_model_len));
     if (need > 0) {
       e->ws_attn_bytes = need;
@@ -658,8 +658,16 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       while (aa.num_decode < B && hm.qsl[aa.num_decode + 1] - hm.qsl[aa.num_decode] == 1) ++aa.num_decode;
       double keys = 0;
       for (int t = 0; t < T; ++t) keys += hm.pos[t] + 1;
+      // keys and values of 64 or 128 numbers, bfloat16: the tcgen05 prompt kernel and the TMA-staged decode kernels of the
+      // Llama family (every head its own key/value head); everything else: the mma.sync / per-row kernels
+      const bool tc = !e->f32 && (h.dim == 64 || h.dim == 128) && h.vdim == h.dim && ldq % 8 == 0 && (bs & (bs - 1)) == 0 && ((uintptr_t)q & 15) == 0 &&
+                      (!decode_only || (e->ws_attn && paged_attn_extras_decode_ok(B, H, H, h.dim, bs)));
+      const int max_seq_bound = decode_only ? max_blocks * bs : 0;
       HFWD(decode_only ? C_ATT_DEC : C_ATT_GEN, (decode_only ? keys : (double)T) * H * (h.dim + h.vdim) * es + (double)T * H * (h.dim + h.vdim) * es,
-           2.0 * keys * H * (h.dim + h.vdim), attn_bias_chunk(aa, st));
+           2.0 * keys * H * (h.dim + h.vdim),
+           tc ? paged_attn_extras(e->mixbuf, q, ldq, L.kc, L.vc, m.btab, max_blocks, m.seq_lens, m.qsl, B, T, aa.max_q, std::max(max_seq_bound, 1), H, H, h.dim, bs,
+                                  h.scale, 0.f, nullptr, e->ws_attn, e->ws_attn_bytes, st)
+              : attn_bias_chunk(aa, st));
       if (h.out_gate) HFWD(C_ACT, (double)T * nv * 3 * es, 0, sigmoid_gate_mul(e->mixbuf, nv, at(e->pbuf, L.lat_g), ldp, T, nv, elt, st));
       DENSE(e->obuf1, d, e->mixbuf, nv, L.o, T, ACT_NONE);
       add_src(e->obuf1, d, 1.f);
@@ -735,7 +743,7 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       const int np = T * h.top;
       // bfloat16 prompt steps with enough routed rows: groups padded to 256 rows for the grouped tensor-core GEMMs
       const int np_pad = (np / 256 + h.experts + 1) * 256;
-      const bool grouped = !ungated && !e->f32 && !decode_only && np >= 512 && h.expert_ff % 64 == 0 && d % 8 == 0 && e->moe_xperm && np_pad <= e->moe_rows_padded;
+      const bool grouped = !e->f32 && !decode_only && np >= 512 && h.expert_ff % 64 == 0 && d % 8 == 0 && e->moe_xperm && np_pad <= e->moe_rows_padded;
       if (grouped) { ra.pad = 256; ra.rows_padded = np_pad; ra.tile_group = e->moe_tile_group; }
       HFWD(C_MOE, Td * es + (double)h.experts * d * es, 2.0 * Td * h.experts, moe_route(ra, st));
       ++e->launches;
@@ -746,8 +754,8 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
         // 256-row tile takes its expert's weights from the stacked tensors.  Nothing comes back to the host.
         const int eff = h.expert_ff;
         HFWD(C_MOE, (double)np_pad * d * 4, 0, moe_gather_rows(e->moe_xperm, e->hx, d, e->moe_ptok, w_out ? nullptr : e->moe_pw, np_pad, d, st));
-        HFWD(C_MOE, 2.0 * (2.0 * h.experts * eff * d + (double)np_pad * (d + eff)), 4.0 * np * (double)eff * d,
-             gemm_grouped(e->moe_hidden, e->moe_xperm, L.e_gate, np_pad, eff, d, h.experts, e->moe_tile_group, clamped ? 1 : 0, 1.702f, h.expert_limit, st));
+        HFWD(C_MOE, 2.0 * ((ungated ? 1.0 : 2.0) * h.experts * eff * d + (double)np_pad * (d + eff)), (ungated ? 2.0 : 4.0) * np * (double)eff * d,
+             gemm_grouped(e->moe_hidden, e->moe_xperm, L.e_gate, np_pad, eff, d, h.experts, e->moe_tile_group, ungated ? -2 : clamped ? 1 : 0, 1.702f, h.expert_limit, st));
         HFWD(C_MOE, 2.0 * ((double)h.experts * eff * d + (double)np_pad * (d + eff)), 2.0 * np * (double)eff * d,
              gemm_grouped(e->moe_operm, e->moe_hidden, L.e_down, np_pad, d, eff, h.experts, e->moe_tile_group, -1, 0.f, 0.f, st));
         HFWD(C_MOE, (double)np * d * 4, 0, moe_scatter_rows(e->moe_out, e->moe_operm, e->moe_pdest, np_pad, d, st));
@@ -758,7 +766,7 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       if (clamped) { g.glu = GLU_CLAMPED_SIGMOID; g.glu_limit = h.expert_limit; }
       if (ungated) { g.w2 = nullptr; g.w_zs = (int64_t)h.expert_ff * d; g.act = ACT_RELU2; }
       g.elt = elt; g.out_f32 = e->f32;
-      HFWD(C_MOE, 2 * wexp + (double)np * (d + h.expert_ff) * es, 4.0 * np * (double)h.expert_ff * d, linear_any(g, st));
+      HFWD(C_MOE, (ungated ? 1 : 2) * wexp + (double)np * (d + h.expert_ff) * es, (ungated ? 2.0 : 4.0) * np * (double)h.expert_ff * d, linear_any(g, st));
       LinearArgs dn;     // experts' down projection, scattered to row (token * top + choice)
       dn.x = e->moe_hidden; dn.ldx = h.expert_ff; dn.w = L.e_down; dn.y = e->moe_out; dn.ldy = d; dn.T = np; dn.N = d; dn.K = h.expert_ff;
       dn.nz = h.experts; dn.w_zs = (int64_t)d * h.expert_ff; dn.group_off = e->moe_goff; dn.max_rows = np; dn.yrows = e->moe_pdest;

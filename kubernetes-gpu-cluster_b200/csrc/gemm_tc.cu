@@ -129,6 +129,7 @@ struct GemmParams {
 __device__ __forceinline__ float apply_act(float v, int act) {
   if (act == 1) return fmaxf(v, 0.f);
   if (act == 3) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+  if (act == 4) { const float r = fmaxf(v, 0.f); return r * r; }
   return v;
 }
 
@@ -1372,7 +1373,7 @@ inline namespace KGE_ELT_NS {
 // Grouped rows (the experts of a mixture, prompt steps): x [T, K] holds every group's rows padded to a multiple of 256,
 // w stacks `groups` weight matrices ([N, K] each, or [2f, K] = [gate | up] with glu >= 0), tile_group (device, T / 256
 // entries) names the matrix of every 256 rows.  y [T, N] (or [T, f]).  One launch for all groups, T > 256.
-// glu: -1 plain projection, 0 silu(gate) * up, 1 the clamped pair.
+// glu: -1 plain projection, -2 plain projection followed by relu(.)^2, 0 silu(gate) * up, 1 the clamped pair.
 int gemm_grouped(void* y, const void* x, const void* w, int T, int N, int K, int groups, const int32_t* tile_group, int glu, float glu_alpha,
                  float glu_limit, cudaStream_t st) {
   const bool gated = glu >= 0;
@@ -1382,7 +1383,7 @@ int gemm_grouped(void* y, const void* x, const void* w, int T, int N, int K, int
   const GemmPlan g = plan_gemm(T, N, K, gated ? 64 : BLK_M);
   KGE_REQUIRE(!g.ws && g.splits == 1 && 256 % g.tokn == 0, "gemm_grouped: internal: unexpected plan");
   GemmParams p;
-  p.y = (bf16*)y; p.bias = nullptr; p.T = T; p.N = N; p.K = K; p.act = gated ? 2 : 0;
+  p.y = (bf16*)y; p.bias = nullptr; p.T = T; p.N = N; p.K = K; p.act = gated ? 2 : (glu == -2 ? 4 : 0);
   p.glu = gated ? glu : 0; p.glu_alpha = glu_alpha; p.glu_limit = glu_limit;
   p.l2_hints = tunable(TUN_GEMM_L2_HINTS); p.trace = g_gemm_trace; p.ws_count = nullptr; p.ws_part = nullptr;
   p.m_tiles = g.m_tiles; p.n_tiles = g.n_tiles; p.splits = g.splits; p.kb_total = g.kb_total; p.kb_per_split = g.kb_per_split;

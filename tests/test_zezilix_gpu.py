@@ -297,6 +297,50 @@ def test_tensor_core_sizes(kge, tmp_path):
     check(got, want, "bfloat16", "", mg, oz.bfloat16_noise(cfg, W, toks))
 
 
+@pytest.mark.parametrize("shape", [(2, 32, 32, 64, True), (3, 96, 32, 128, False), (1, 64, 64, 128, True), (2, 16, 48, 64, False)])
+def test_tensor_core_head_sizes(kge, tmp_path, shape):
+    """bfloat16, 64-token pages, latent attention alone with keys and values of 64 or 128 numbers (unrotated + rotated
+    part; values as wide as the keys): the sizes the tcgen05 prompt kernel and the TMA-staged decode kernels take.  Prompt
+    steps, pieces, decoding over a page border, a decode batch of unequal contexts, single tokens beside a prompt piece."""
+    heads, dim, rot_dim, vdim, gated = shape
+    L = oz.latent_layer(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=24, q_rank=40, gated=gated, scale=1.6 / (dim + rot_dim) ** 0.5, mlp=None)
+    cfg = oz.make_config([L], width=64, loop=(0, 1, 2))
+    W = oz.make_weights(cfg, seed=23)
+    toks = prompt(cfg, 230, 34)
+    want = oz.forward(cfg, W, toks)
+    noise = oz.bfloat16_noise(cfg, W, toks)
+    llm = make_engine(kge, tmp_path, cfg, W, "bfloat16", bs=64, tokens=1024)
+    check(run_pieces(llm, 0, toks, [230]), want, "bfloat16", "whole", None, noise)
+    llm.trace_end(0)
+    got = np.concatenate([run_pieces(llm, 1, toks[:180], [61, 3, 2, 64, 50]), run_pieces(llm, 1, toks[180:], [1] * 50)])
+    check(got, want, "bfloat16", "pieces, then decoding", None, noise)
+    # two requests decoding side by side (one far longer than the other) and a third that brings a prompt piece
+    a, b = prompt(cfg, 150, 35), prompt(cfg, 9, 36)
+    wa, wb = oz.forward(cfg, W, a).numpy(), oz.forward(cfg, W, b).numpy()
+    llm.trace_add(2, a[:140])
+    llm.trace_add(3, b[:3])
+    llm.trace_step([(2, 140, []), (3, 3, [])])
+    ga, gb = [], []
+    for i in range(6):
+        llm.trace_add(2, a[140 + i:141 + i])
+        llm.trace_add(3, b[3 + i:4 + i])
+        lg = llm.trace_step([(2, 1, [0]), (3, 1, [0])])
+        ga.append(lg[0])
+        gb.append(lg[1])
+    c, d1 = prompt(cfg, 70, 37), prompt(cfg, 1, 38)
+    llm.trace_end(3)
+    llm.trace_add(2, a[146:147])
+    llm.trace_add(4, c[:66])
+    llm.trace_add(5, d1)
+    lg = llm.trace_step([(2, 1, [0]), (4, 66, list(range(66))), (5, 1, [0])])
+    llm.close()
+    check(np.stack(ga), wa[140:146], "bfloat16", "long request of a decode batch", None, noise)
+    check(np.stack(gb), wb[3:9], "bfloat16", "short request of a decode batch", None, noise)
+    check(lg[:1], wa[146:147], "bfloat16", "a single token beside a prompt piece", None, noise)
+    check(lg[1:67], oz.forward(cfg, W, c).numpy()[:66], "bfloat16", "a prompt piece beside single tokens", None, noise)
+    check(lg[67:], oz.forward(cfg, W, d1).numpy(), "bfloat16", "a lone first token in a mixed step", None, noise)
+
+
 def test_first_tokens(kge, tmp_path):
     cfg = full()
     W = oz.make_weights(cfg, seed=11)
