@@ -521,10 +521,11 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
   };
   if (hyper) HFWD(C_EMBED, Td * (es + 4.0 * S), 0, embed_norm_streams(e->res32, m.ids, e->embed, s.embed_norm ? e->embed_norm_w : nullptr, T, d, S, s.eps, elt, st));
   else HFWD(C_EMBED, Td * (es + 4), 0, embed_f32(e->res32, m.ids, e->embed, T, d, elt, st));
+  bool hx_ready = false;      // the previous layer's last write of the streams already formed this layer's normed input
   for (int i = 0; i < s.L; ++i) {
     const HybridLayerSpec& h = s.hybrid[i];
     const HybridLayerW& L = e->hyb[i];
-    if (hyper) HFWD(C_NORM, Td * (4.0 * S + es), 0, stream_read(e->hx, L.hc_in[0], nullptr, L.norm1, T, 1.f, nullptr));
+    if (hyper) { if (!hx_ready) HFWD(C_NORM, Td * (4.0 * S + es), 0, stream_read(e->hx, L.hc_in[0], nullptr, L.norm1, T, 1.f, nullptr)); hx_ready = false; }
     else HFWD(C_NORM, Td * (4 + es), 0, layer_norm(e->hx, nullptr, L.norm1, T, 1.f));
     CombineArgs cb;
     bool y32_used = false;
@@ -544,11 +545,15 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       cb = CombineArgs();
       return rc;
     };
+    // the write of the streams also forms the next sublayer's normed input (the feed-forward's, or the next layer's mixer's)
     auto flush = [&]() -> int {
       if (!hyper) return flush_more();
       StreamCombineArgs sc;
       sc.xs = e->res32; sc.src = cb; sc.y32 = y32_used ? e->y32 : nullptr; sc.col_scale = L.col_scale[sub]; sc.mix = L.hc_mix[sub]; sc.out_w = L.hc_out[sub];
-      sc.mult = s.residual_mult; sc.T = T; sc.d = d; sc.S = S; sc.elt = elt;
+      sc.mult = s.residual_mult; sc.T = T; sc.d = d; sc.S = S; sc.elt = elt; sc.eps = s.eps;
+      const bool mixer_done = sub == 0 && h.mlp != HybridLayerSpec::NONE;
+      if (mixer_done) { sc.next_in = L.hc_in[1]; sc.next_w = L.norm2; sc.next_y = e->hx; }
+      else if (i + 1 < s.L) { sc.next_in = e->hyb[i + 1].hc_in[0]; sc.next_w = e->hyb[i + 1].norm1; sc.next_y = e->hx; hx_ready = true; }
       cb = CombineArgs(); y32_used = false;
       return stream_combine(sc, st);
     };
@@ -611,6 +616,7 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       wa.h = e->hx; wa.ldh = d; wa.mu = L.wkv_mu; wa.mixes = e->mixes; wa.nmix = 5; wa.d = d;
       wa.state = e->state + L.state_off; wa.slot_stride = e->slot_stride; wa.slots = m.sslot; wa.qsl = m.qsl; wa.positions = m.pos; wa.token_req = m.treq;
       wa.B = B; wa.T = T; wa.H = h.heads; wa.dim = h.dim; wa.eps = s.eps; wa.elt = elt;
+      for (int r = 0; r < B; ++r) wa.max_q = std::max(wa.max_q, hm.qsl[r + 1] - hm.qsl[r]);
       HFWD(C_MLSTM, Td * 6 * es, 0, wkv_shift_mix(wa, st));
       ++e->launches;
       for (int z = 0; z < 4; ++z) {                      // r, k, v and the gate, each from its own blend
@@ -708,8 +714,7 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       // the feed-forward reads a norm of the stream that already holds the mixer's output
       { const double nsrc = cb.n; HFWD(C_ACT, Td * (8.0 * S + nsrc * es), 0, flush()); }
       sub = 1;
-      if (hyper) HFWD(C_NORM, Td * (4.0 * S + es), 0, stream_read(e->hx, L.hc_in[1], nullptr, L.norm2, T, 1.f, nullptr));
-      else HFWD(C_NORM, Td * (4 + es), 0, layer_norm(e->hx, nullptr, L.norm2, T, 1.f));
+      if (!hyper) HFWD(C_NORM, Td * (4 + es), 0, layer_norm(e->hx, nullptr, L.norm2, T, 1.f));
     }
     if (h.mlp == HybridLayerSpec::DENSE && h.ff_limit > 0.f) {
       // clamped gated unit: bfloat16 forms the pair in the epilogue of the tensor-core GEMM over [gate | up]

@@ -196,6 +196,8 @@ struct StreamCombineArgs {
   float* xs = nullptr; CombineArgs src; const float* y32 = nullptr;
   const float* col_scale = nullptr; const float* mix = nullptr; const float* out_w = nullptr;
   float mult = 1.f; int T = 0, d = 0, S = 1; int elt = KGE_ELT_BF16;
+  // the next sublayer's read in the same pass (next_y != null): next_y[t, :] = n(sum_j next_in[j] * new xs[t, j, :]) * next_w
+  const float* next_in = nullptr; const void* next_w = nullptr; void* next_y = nullptr; float eps = 1e-5f;
 };
 int stream_combine(const StreamCombineArgs& a, cudaStream_t st);
 
@@ -215,6 +217,7 @@ struct WkvArgs {
   float* state = nullptr; int64_t slot_stride = 0;     // this layer's part of slot 0: [d] saved row, then [H, dim, dim]
   const int32_t* slots = nullptr; const int32_t* qsl = nullptr; const int32_t* positions = nullptr; const int32_t* token_req = nullptr;
   int B = 0, T = 0, H = 0, dim = 0;
+  int max_q = 0;                           // the longest request's rows in this step (0 = unknown: token by token)
   float eps = 1e-5f;
   int elt = KGE_ELT_BF16;
 };

@@ -90,13 +90,16 @@ template <typename E>
 __global__ void __launch_bounds__(256) stream_combine_kernel(StreamCombineArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float mix[SMAX * SMAX], wout[SMAX], rs[4];
+  extern __shared__ float un[];                  // the next sublayer's input row before its norm (only with next_y)
+  __shared__ float mix[SMAX * SMAX], wout[SMAX], win[SMAX], rs[4], red[33];
   const int t = blockIdx.x, d = a.d, S = a.S;
+  if (threadIdx.x < S) win[threadIdx.x] = a.next_in ? a.next_in[threadIdx.x] : 1.f;
   if (threadIdx.x < S * S) mix[threadIdx.x] = a.mix ? a.mix[threadIdx.x] : (threadIdx.x / S == threadIdx.x % S ? 1.f : 0.f);
   if (threadIdx.x < S) wout[threadIdx.x] = a.out_w ? a.out_w[threadIdx.x] : 1.f;
   if (threadIdx.x < a.src.n) rs[threadIdx.x] = a.src.scale[threadIdx.x] * (a.src.rscale[threadIdx.x] ? a.src.rscale[threadIdx.x][(int64_t)t * a.src.rs_stride[threadIdx.x]] : 1.f);
   __syncthreads();
   float* x = a.xs + (int64_t)t * S * d;
+  float ss = 0.f;
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
     float y = a.y32 ? a.y32[(int64_t)t * d + c] : 0.f;
     for (int i = 0; i < a.src.n; ++i) y = fmaf(rs[i], ldf((const E*)a.src.src[i] + (int64_t)t * a.src.ld[i] + c), y);
@@ -104,23 +107,39 @@ __global__ void __launch_bounds__(256) stream_combine_kernel(StreamCombineArgs a
     float old[SMAX];
 #pragma unroll
     for (int s = 0; s < SMAX; ++s) old[s] = s < S ? x[(int64_t)s * d + c] : 0.f;
+    float u = 0.f;
 #pragma unroll
     for (int j = 0; j < SMAX; ++j) {
       if (j < S) {
         float v = 0.f;
 #pragma unroll
         for (int s = 0; s < SMAX; ++s) if (s < S) v = fmaf(mix[s * S + j], old[s], v);
-        x[(int64_t)j * d + c] = fmaf(wout[j], z, v);
+        v = fmaf(wout[j], z, v);
+        x[(int64_t)j * d + c] = v;
+        u = j == 0 ? win[0] * v : fmaf(win[j], v, u);      // the same order of summation as stream_norm
       }
     }
+    if (a.next_y) { un[c] = u; ss = fmaf(u, u, ss); }
   }
+  if (!a.next_y) return;
+  const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)d + a.eps);
+  E* y2 = (E*)a.next_y + (int64_t)t * d;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) stf(y2 + c, un[c] * inv * ldf((const E*)a.next_w + c));
 }
 
 int stream_combine(const StreamCombineArgs& a, cudaStream_t st) {
   if (a.T <= 0) return 0;
   KGE_REQUIRE(a.S >= 1 && a.S <= SMAX && a.src.n >= 0 && a.src.n <= 4, "stream_combine: %d streams, %d sources", a.S, a.src.n);
-  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(stream_combine_kernel<float>, dim3(a.T), dim3(256), 0, st, a)
-                                        : launch_pdl(stream_combine_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), 0, st, a);
+  const size_t smem = a.next_y ? (size_t)a.d * 4 : 0;
+  KGE_REQUIRE(smem <= 200 * 1024, "stream_combine: rows of %d columns", a.d);
+  static size_t smem_set = 0;
+  if (smem > 48 * 1024 && smem > smem_set) {
+    KGE_CUDA_OK(cudaFuncSetAttribute(stream_combine_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    KGE_CUDA_OK(cudaFuncSetAttribute(stream_combine_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    smem_set = smem;
+  }
+  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(stream_combine_kernel<float>, dim3(a.T), dim3(256), smem, st, a)
+                                        : launch_pdl(stream_combine_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), smem, st, a);
   KGE_CUDA_OK(ce);
   return 0;
 }
