@@ -70,6 +70,114 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(StreamNormArgs a) {
   }
 }
 
+// the same arithmetic as stream_norm_kernel, column for column, four columns per thread and pass
+template <typename E>
+__global__ void __launch_bounds__(256) stream_norm_vec_kernel(StreamNormArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float u[];
+  __shared__ float red[33];
+  __shared__ float win[SMAX];
+  const int r = blockIdx.x, row = a.rows ? a.rows[r] : r, d = a.d, S = a.S;
+  if (threadIdx.x < S) win[threadIdx.x] = a.in_w ? a.in_w[threadIdx.x] : 1.f;
+  __syncthreads();
+  const float* x = a.xs + (int64_t)row * S * d;
+  float ss = 0.f;
+  for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+    float v[4], t[4];
+    ld4(x + c, v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = win[0] * v[i];
+    for (int s = 1; s < S; ++s) {
+      ld4(x + (int64_t)s * d + c, t);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] = fmaf(win[s], t[i], v[i]);
+    }
+    st4(u + c, v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ss = fmaf(v[i], v[i], ss);
+  }
+  const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)d + a.eps) * a.out_scale;
+  E* y = (E*)a.y + (int64_t)r * d;
+  for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+    float v[4], w[4];
+    ld4(u + c, v);
+    if (a.y) {
+      ld4((const E*)a.w + c, w);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) w[i] = v[i] * inv * w[i];
+      st4(y + c, w);
+    }
+    if (a.sum_out) st4(a.sum_out + (int64_t)r * d + c, v);
+  }
+}
+
+template <typename E>
+__global__ void __launch_bounds__(256) stream_combine_vec_kernel(StreamCombineArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float un[];
+  __shared__ float mix[SMAX * SMAX], wout[SMAX], win[SMAX], rs[4], red[33];
+  const int t = blockIdx.x, d = a.d, S = a.S;
+  if (threadIdx.x < S) win[threadIdx.x] = a.next_in ? a.next_in[threadIdx.x] : 1.f;
+  if (threadIdx.x < S * S) mix[threadIdx.x] = a.mix ? a.mix[threadIdx.x] : (threadIdx.x / S == threadIdx.x % S ? 1.f : 0.f);
+  if (threadIdx.x < S) wout[threadIdx.x] = a.out_w ? a.out_w[threadIdx.x] : 1.f;
+  if (threadIdx.x < a.src.n) rs[threadIdx.x] = a.src.scale[threadIdx.x] * (a.src.rscale[threadIdx.x] ? a.src.rscale[threadIdx.x][(int64_t)t * a.src.rs_stride[threadIdx.x]] : 1.f);
+  __syncthreads();
+  float* x = a.xs + (int64_t)t * S * d;
+  float ss = 0.f;
+  for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+    float y[4] = {0.f, 0.f, 0.f, 0.f}, q[4];
+    if (a.y32) ld4(a.y32 + (int64_t)t * d + c, y);
+    for (int i = 0; i < a.src.n; ++i) {
+      ld4((const E*)a.src.src[i] + (int64_t)t * a.src.ld[i] + c, q);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) y[k] = fmaf(rs[i], q[k], y[k]);
+    }
+    float z[4] = {1.f, 1.f, 1.f, 1.f};
+    if (a.col_scale) ld4(a.col_scale + c, z);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) z[k] = a.mult * z[k] * y[k];
+    float old[SMAX][4];
+#pragma unroll
+    for (int s = 0; s < SMAX; ++s) if (s < S) ld4(x + (int64_t)s * d + c, old[s]);
+    float u[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < SMAX; ++j) {
+      if (j < S) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s)
+          if (s < S) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] = fmaf(mix[s * S + j], old[s][k], v[k]);
+          }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { v[k] = fmaf(wout[j], z[k], v[k]); u[k] = j == 0 ? win[0] * v[k] : fmaf(win[j], v[k], u[k]); }
+        st4(x + (int64_t)j * d + c, v);
+      }
+    }
+    if (a.next_y) {
+      st4(un + c, u);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) ss = fmaf(u[k], u[k], ss);
+    }
+  }
+  if (!a.next_y) return;
+  const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)d + a.eps);
+  E* y2 = (E*)a.next_y + (int64_t)t * d;
+  for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+    float v[4], w[4];
+    ld4(un + c, v);
+    ld4((const E*)a.next_w + c, w);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) w[k] = v[k] * inv * w[k];
+    st4(y2 + c, w);
+  }
+}
+
+static bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 int stream_norm(const StreamNormArgs& a, cudaStream_t st) {
   if (a.R <= 0) return 0;
   KGE_REQUIRE(a.S >= 1 && a.S <= SMAX && a.d > 0 && (size_t)a.d * 4 <= 200 * 1024, "stream_norm: %d streams of %d columns", a.S, a.d);
@@ -78,10 +186,18 @@ int stream_norm(const StreamNormArgs& a, cudaStream_t st) {
   if (smem > 48 * 1024 && smem > smem_set) {
     KGE_CUDA_OK(cudaFuncSetAttribute(stream_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     KGE_CUDA_OK(cudaFuncSetAttribute(stream_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    smem_set = smem;
   }
-  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(stream_norm_kernel<float>, dim3(a.R), dim3(256), smem, st, a)
-                                        : launch_pdl(stream_norm_kernel<__nv_bfloat16>, dim3(a.R), dim3(256), smem, st, a);
+  const bool vec = a.d % 8 == 0 && al16(a.xs) && al16(a.y) && al16(a.w) && al16(a.sum_out);
+  if (vec && smem > 48 * 1024 && smem > smem_set) {
+    KGE_CUDA_OK(cudaFuncSetAttribute(stream_norm_vec_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    KGE_CUDA_OK(cudaFuncSetAttribute(stream_norm_vec_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  }
+  if (smem > 48 * 1024 && smem > smem_set) smem_set = smem;
+  cudaError_t ce;
+  if (vec) ce = a.elt == KGE_ELT_F32 ? launch_pdl(stream_norm_vec_kernel<float>, dim3(a.R), dim3(256), smem, st, a)
+                                     : launch_pdl(stream_norm_vec_kernel<__nv_bfloat16>, dim3(a.R), dim3(256), smem, st, a);
+  else ce = a.elt == KGE_ELT_F32 ? launch_pdl(stream_norm_kernel<float>, dim3(a.R), dim3(256), smem, st, a)
+                                 : launch_pdl(stream_norm_kernel<__nv_bfloat16>, dim3(a.R), dim3(256), smem, st, a);
   KGE_CUDA_OK(ce);
   return 0;
 }
@@ -136,10 +252,19 @@ int stream_combine(const StreamCombineArgs& a, cudaStream_t st) {
   if (smem > 48 * 1024 && smem > smem_set) {
     KGE_CUDA_OK(cudaFuncSetAttribute(stream_combine_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     KGE_CUDA_OK(cudaFuncSetAttribute(stream_combine_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    smem_set = smem;
   }
-  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(stream_combine_kernel<float>, dim3(a.T), dim3(256), smem, st, a)
-                                        : launch_pdl(stream_combine_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), smem, st, a);
+  bool vec = a.d % 8 == 0 && al16(a.xs) && al16(a.y32) && al16(a.col_scale) && al16(a.next_y) && al16(a.next_w);
+  for (int i = 0; i < a.src.n; ++i) vec = vec && al16(a.src.src[i]) && a.src.ld[i] % 8 == 0;
+  if (vec && smem > 48 * 1024 && smem > smem_set) {
+    KGE_CUDA_OK(cudaFuncSetAttribute(stream_combine_vec_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    KGE_CUDA_OK(cudaFuncSetAttribute(stream_combine_vec_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  }
+  if (smem > 48 * 1024 && smem > smem_set) smem_set = smem;
+  cudaError_t ce;
+  if (vec) ce = a.elt == KGE_ELT_F32 ? launch_pdl(stream_combine_vec_kernel<float>, dim3(a.T), dim3(256), smem, st, a)
+                                     : launch_pdl(stream_combine_vec_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), smem, st, a);
+  else ce = a.elt == KGE_ELT_F32 ? launch_pdl(stream_combine_kernel<float>, dim3(a.T), dim3(256), smem, st, a)
+                                 : launch_pdl(stream_combine_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), smem, st, a);
   KGE_CUDA_OK(ce);
   return 0;
 }

@@ -31,6 +31,30 @@ __global__ void __launch_bounds__(256) wkv_shift_mix_kernel(WkvArgs a) {
   }
 }
 
+// the same, four columns per thread and pass (rows of 16-byte multiples)
+template <typename E>
+__global__ void __launch_bounds__(256) wkv_shift_mix_vec_kernel(WkvArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, b = a.token_req[t], d = a.d;
+  const bool first = t == a.qsl[b];
+  const bool zero = first && a.positions[t] == 0;
+  const E* h = (const E*)a.h + (int64_t)t * a.ldh;
+  const E* hp = (const E*)a.h + (int64_t)(t - 1) * a.ldh;
+  const float* sp = a.state + (int64_t)a.slots[b] * a.slot_stride;
+  for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+    float x[4], p[4] = {0.f, 0.f, 0.f, 0.f}, m[4], o[4];
+    ld4(h + c, x);
+    if (!zero) { if (first) ld4(sp + c, p); else ld4(hp + c, p); }
+    for (int z = 0; z < a.nmix; ++z) {
+      ld4((const E*)a.mu + (int64_t)z * d + c, m);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[i] = fmaf(p[i] - x[i], m[i], x[i]);
+      st4((E*)a.mixes + ((int64_t)z * a.T + t) * d + c, o);
+    }
+  }
+}
+
 // after the blends: the slot keeps the last row of every request of the step
 template <typename E>
 __global__ void __launch_bounds__(256) wkv_save_row_kernel(WkvArgs a) {
@@ -45,6 +69,15 @@ __global__ void __launch_bounds__(256) wkv_save_row_kernel(WkvArgs a) {
 
 int wkv_shift_mix(const WkvArgs& a, cudaStream_t st) {
   if (a.T <= 0) return 0;
+  const bool vec = a.d % 8 == 0 && a.ldh % 8 == 0 && a.slot_stride % 4 == 0 && ((reinterpret_cast<uintptr_t>(a.h) | reinterpret_cast<uintptr_t>(a.mu) | reinterpret_cast<uintptr_t>(a.mixes) | reinterpret_cast<uintptr_t>(a.state)) & 15) == 0;
+  if (vec) {
+    cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(wkv_shift_mix_vec_kernel<float>, dim3(a.T), dim3(256), 0, st, a)
+                                          : launch_pdl(wkv_shift_mix_vec_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), 0, st, a);
+    KGE_CUDA_OK(ce);
+    ce = a.elt == KGE_ELT_F32 ? launch_pdl(wkv_save_row_kernel<float>, dim3(a.B), dim3(256), 0, st, a) : launch_pdl(wkv_save_row_kernel<__nv_bfloat16>, dim3(a.B), dim3(256), 0, st, a);
+    KGE_CUDA_OK(ce);
+    return 0;
+  }
   if (a.elt == KGE_ELT_F32) {
     KGE_CUDA_OK(launch_pdl(wkv_shift_mix_kernel<float>, dim3(a.T), dim3(256), 0, st, a));
     KGE_CUDA_OK(launch_pdl(wkv_save_row_kernel<float>, dim3(a.B), dim3(256), 0, st, a));
@@ -115,21 +148,21 @@ __global__ void __launch_bounds__(MAXD) wkv_scan_kernel(WkvArgs a) {
 //     o_t = sum_k r_tk e^{L_(t-1)k} S_k. + sum_{j<t} (sum_k r_tk k_jk e^{L_(t-1)k - L_jk}) v_j + (sum_k r_tk u_k k_tk) v_t
 //     S  <- diag(e^{L_last}) S + sum_j (k_j e^{L_last - L_j}) v_j^T
 // Every exponent is a sum of log decays of tokens between the two positions, so it is <= 0 and nothing overflows however
-// fast a channel forgets.  One block of 128 threads per (request, head), head sizes up to 64 (a multiple of 4): the
-// read-out and the state update are 4 x 4 / 8 x 4 register tiles over shared operands; the state stays in registers
+// fast a channel forgets.  One block of 256 threads per (request, head), head sizes up to 64 (a multiple of 4): the
+// read-out and the state update are 2 x 4 / 4 x 4 register tiles over shared operands; the state stays in registers
 // across chunks (mirrored in shared memory for the read-out).  A request's last chunk may be short.
 constexpr int WC = 32, WD = 64, WLD = WD + 4, WLC = WC + 4;
 constexpr size_t WKV_CHUNK_SMEM = (size_t)(5 * WC * WLD + WD * WLC + WC * WLC + WD * WLD + 2 * WD) * 4;
 
-template <typename E, bool FAST>
-__global__ void __launch_bounds__(128) wkv_chunk_kernel(WkvArgs a) {
+template <typename E>
+__global__ void __launch_bounds__(256) wkv_chunk_kernel(WkvArgs a) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float sm[];
   float* rs = sm;                       // [WC][WLD] r
   float* ks = rs + WC * WLD;            // [WC][WLD] k
   float* vs = ks + WC * WLD;            // [WC][WLD] v
-  float* Ls = vs + WC * WLD;            // [WC][WLD] log decays (times log2 e), then their running sums
+  float* Ls = vs + WC * WLD;            // [WC][WLD] log decays (in units of log 2), then their running sums
   float* kd = Ls + WC * WLD;            // [WC][WLD] k_j e^{L_last - L_j}
   float* rdT = kd + WC * WLD;           // [WD][WLC] r_t e^{L_(t-1)}, transposed
   float* PT = rdT + WD * WLC;           // [WC][WLC] scores, transposed: PT[j][t]
@@ -141,22 +174,21 @@ __global__ void __launch_bounds__(128) wkv_chunk_kernel(WkvArgs a) {
   if (r0 >= r1) return;
   const bool fresh = a.positions[r0] == 0;
   float* Sg = a.state + (int64_t)a.slots[b] * a.slot_stride + a.d + (int64_t)h * dim * dim;
-  const int kg = tid >> 4, vg = tid & 15;          // this thread's state tile: rows kg * 8 .., columns vg * 4 ..
-  float S[8][4];
+  const int kg = tid >> 4, vg = tid & 15;          // this thread's state tile: rows kg * 4 .., columns vg * 4 ..
+  float S[4][4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int k = kg * 8 + i, v = vg * 4 + j;
+      const int k = kg * 4 + i, v = vg * 4 + j;
       S[i][j] = (!fresh && k < dim && v < dim) ? Sg[(int64_t)k * dim + v] : 0.f;
     }
   if (tid < WD) us[tid] = tid < dim ? a.u[h * dim + tid] : 0.f;
   const E *rp = (const E*)a.r, *kp = (const E*)a.k, *vp = (const E*)a.v;
-  auto ex = [](float x) { return FAST ? exp2f(x) : exp2f(x); };      // exponents are kept in units of log 2
   for (int c0 = r0; c0 < r1; c0 += WC) {
     const int n = min(WC, r1 - c0);
     __syncthreads();                               // the previous chunk's readers are done
-    for (int i = tid; i < WC * WD; i += 128) {
+    for (int i = tid; i < WC * WD; i += 256) {
       const int t = i / WD, c = i % WD;
       const bool ok = t < n && c < dim;
       const int64_t o = (int64_t)(c0 + t) * a.ld + h * dim + c;
@@ -166,95 +198,98 @@ __global__ void __launch_bounds__(128) wkv_chunk_kernel(WkvArgs a) {
       Ls[t * WLD + c] = ok ? -expf(a.decay_pre[(int64_t)(c0 + t) * HD + h * dim + c]) * 1.4426950408889634f : 0.f;
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) *reinterpret_cast<float4*>(Ss + (kg * 8 + i) * WLD + vg * 4) = make_float4(S[i][0], S[i][1], S[i][2], S[i][3]);
+    for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(Ss + (kg * 4 + i) * WLD + vg * 4) = make_float4(S[i][0], S[i][1], S[i][2], S[i][3]);
     __syncthreads();
     if (tid < WD) {                                // running sums per channel
       float acc = 0.f;
+#pragma unroll 8
       for (int t = 0; t < WC; ++t) { acc += Ls[t * WLD + tid]; Ls[t * WLD + tid] = acc; }
-      el[tid] = ex(acc);
+      el[tid] = exp2f(acc);
     }
     __syncthreads();
-    for (int i = tid; i < WC * WD; i += 128) {
+    for (int i = tid; i < WC * WD; i += 256) {
       const int t = i / WD, c = i % WD;
       const float lm1 = t > 0 ? Ls[(t - 1) * WLD + c] : 0.f;
-      rdT[c * WLC + t] = rs[t * WLD + c] * ex(lm1);
-      kd[t * WLD + c] = ks[t * WLD + c] * ex(Ls[(WC - 1) * WLD + c] - Ls[t * WLD + c]);
+      rdT[c * WLC + t] = rs[t * WLD + c] * exp2f(lm1);
+      kd[t * WLD + c] = ks[t * WLD + c] * exp2f(Ls[(WC - 1) * WLD + c] - Ls[t * WLD + c]);
     }
     {
-      // scores: thread (t, j mod 4) walks its keys j <= t
-      const int t = tid >> 2, jq = tid & 3;
+      // scores: thread (t, j mod 8) walks its keys j <= t
+      const int t = tid >> 3, jq = tid & 7;
       const float* rt = rs + t * WLD;
       const float* lt = Ls + (t - 1) * WLD;        // read only for j < t, so t >= 1
-      for (int j = jq; j < WC; j += 4) {
+      for (int j = jq; j < WC; j += 8) {
         float acc = 0.f;
         if (j < t) {
           const float *kj = ks + j * WLD, *lj = Ls + j * WLD;
-#pragma unroll 8
-          for (int c = 0; c < WD; ++c) acc = fmaf(rt[c] * kj[c], ex(lt[c] - lj[c]), acc);
+#pragma unroll 4
+          for (int c = 0; c < WD; c += 4) {
+            const float4 r4 = *reinterpret_cast<const float4*>(rt + c), k4 = *reinterpret_cast<const float4*>(kj + c);
+            const float4 a4 = *reinterpret_cast<const float4*>(lt + c), b4 = *reinterpret_cast<const float4*>(lj + c);
+            acc = fmaf(r4.x * k4.x, exp2f(a4.x - b4.x), acc); acc = fmaf(r4.y * k4.y, exp2f(a4.y - b4.y), acc);
+            acc = fmaf(r4.z * k4.z, exp2f(a4.z - b4.z), acc); acc = fmaf(r4.w * k4.w, exp2f(a4.w - b4.w), acc);
+          }
         } else if (j == t) {
           const float* kj = ks + j * WLD;
-#pragma unroll 8
-          for (int c = 0; c < WD; ++c) acc = fmaf(rt[c] * us[c], kj[c], acc);
+#pragma unroll 4
+          for (int c = 0; c < WD; c += 4) {
+            const float4 r4 = *reinterpret_cast<const float4*>(rt + c), k4 = *reinterpret_cast<const float4*>(kj + c), u4 = *reinterpret_cast<const float4*>(us + c);
+            acc = fmaf(r4.x * u4.x, k4.x, acc); acc = fmaf(r4.y * u4.y, k4.y, acc); acc = fmaf(r4.z * u4.z, k4.z, acc); acc = fmaf(r4.w * u4.w, k4.w, acc);
+          }
         }
         PT[j * WLC + t] = acc;
       }
     }
     __syncthreads();
     {
-      // read-out: rows tg * 4 .., columns vg * 4 ..: the carried state, then the chunk's own keys
+      // read-out: rows tg * 2 .., columns vg * 4 ..: the carried state, then the chunk's own keys
       const int tg = tid >> 4;
-      float o[4][4] = {};
-#pragma unroll 4
+      float o[2][4] = {};
+#pragma unroll 8
       for (int k = 0; k < WD; ++k) {
-        const float4 r4 = *reinterpret_cast<const float4*>(rdT + k * WLC + tg * 4);
+        const float2 r2 = *reinterpret_cast<const float2*>(rdT + k * WLC + tg * 2);
         const float4 s4 = *reinterpret_cast<const float4*>(Ss + k * WLD + vg * 4);
-        const float rr[4] = {r4.x, r4.y, r4.z, r4.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) o[i][j] = fmaf(rr[i], sv[j], o[i][j]);
+        o[0][0] = fmaf(r2.x, s4.x, o[0][0]); o[0][1] = fmaf(r2.x, s4.y, o[0][1]); o[0][2] = fmaf(r2.x, s4.z, o[0][2]); o[0][3] = fmaf(r2.x, s4.w, o[0][3]);
+        o[1][0] = fmaf(r2.y, s4.x, o[1][0]); o[1][1] = fmaf(r2.y, s4.y, o[1][1]); o[1][2] = fmaf(r2.y, s4.z, o[1][2]); o[1][3] = fmaf(r2.y, s4.w, o[1][3]);
       }
-      const int jmax = min(tg * 4 + 4, n);
+      const int jmax = min(tg * 2 + 2, n);
       for (int j = 0; j < jmax; ++j) {
-        const float4 p4 = *reinterpret_cast<const float4*>(PT + j * WLC + tg * 4);
+        const float2 p2 = *reinterpret_cast<const float2*>(PT + j * WLC + tg * 2);
         const float4 v4 = *reinterpret_cast<const float4*>(vs + j * WLD + vg * 4);
-        const float pp[4] = {p4.x, p4.y, p4.z, p4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj) o[i][jj] = fmaf(pp[i], vv[jj], o[i][jj]);
+        o[0][0] = fmaf(p2.x, v4.x, o[0][0]); o[0][1] = fmaf(p2.x, v4.y, o[0][1]); o[0][2] = fmaf(p2.x, v4.z, o[0][2]); o[0][3] = fmaf(p2.x, v4.w, o[0][3]);
+        o[1][0] = fmaf(p2.y, v4.x, o[1][0]); o[1][1] = fmaf(p2.y, v4.y, o[1][1]); o[1][2] = fmaf(p2.y, v4.z, o[1][2]); o[1][3] = fmaf(p2.y, v4.w, o[1][3]);
       }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int t = tg * 4 + i;
+      for (int i = 0; i < 2; ++i) {
+        const int t = tg * 2 + i;
         if (t < n && vg * 4 < dim) *reinterpret_cast<float4*>(a.o32 + (int64_t)(c0 + t) * HD + h * dim + vg * 4) = make_float4(o[i][0], o[i][1], o[i][2], o[i][3]);
       }
     }
     {
       // the state moves to the chunk's end
-      float e8[8];
+      const float4 e4 = *reinterpret_cast<const float4*>(el + kg * 4);
+      const float ee[4] = {e4.x, e4.y, e4.z, e4.w};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) e8[i] = el[kg * 8 + i];
+      for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) S[i][j] *= e8[i];
+        for (int j = 0; j < 4; ++j) S[i][j] *= ee[i];
+#pragma unroll 4
       for (int j = 0; j < n; ++j) {
-        const float4 ka = *reinterpret_cast<const float4*>(kd + j * WLD + kg * 8), kb = *reinterpret_cast<const float4*>(kd + j * WLD + kg * 8 + 4);
+        const float4 k4 = *reinterpret_cast<const float4*>(kd + j * WLD + kg * 4);
         const float4 v4 = *reinterpret_cast<const float4*>(vs + j * WLD + vg * 4);
-        const float kk[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+        const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) S[i][jj] = fmaf(kk[i], vv[jj], S[i][jj]);
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int k = kg * 8 + i, v = vg * 4 + j;
+      const int k = kg * 4 + i, v = vg * 4 + j;
       if (k < dim && v < dim) Sg[(int64_t)k * dim + v] = S[i][j];
     }
 }
@@ -287,12 +322,11 @@ static int wkv_scan_t(const WkvArgs& a, cudaStream_t st) {
   if (a.max_q >= 8 && a.dim <= WD && a.dim % 4 == 0) {
     static bool smem_set = false;
     if (!smem_set) {
-      KGE_CUDA_OK(cudaFuncSetAttribute(wkv_chunk_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WKV_CHUNK_SMEM));
-      KGE_CUDA_OK(cudaFuncSetAttribute(wkv_chunk_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WKV_CHUNK_SMEM));
+      KGE_CUDA_OK(cudaFuncSetAttribute(wkv_chunk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WKV_CHUNK_SMEM));
+      KGE_CUDA_OK(cudaFuncSetAttribute(wkv_chunk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WKV_CHUNK_SMEM));
       smem_set = true;
     }
-    ce = sizeof(E) == 4 ? launch_pdl(wkv_chunk_kernel<float, false>, grid, dim3(128), WKV_CHUNK_SMEM, st, a)
-                        : launch_pdl(wkv_chunk_kernel<__nv_bfloat16, true>, grid, dim3(128), WKV_CHUNK_SMEM, st, a);
+    ce = launch_pdl(wkv_chunk_kernel<E>, grid, dim3(256), WKV_CHUNK_SMEM, st, a);
   } else if (a.dim <= 32) ce = launch_pdl(wkv_scan_kernel<E, 32>, grid, dim3(32), 0, st, a);
   else if (a.dim <= 64) ce = launch_pdl(wkv_scan_kernel<E, 64>, grid, dim3(64), 0, st, a);
   else if (a.dim <= 128) ce = launch_pdl(wkv_scan_kernel<E, 128>, grid, dim3(128), 0, st, a);
