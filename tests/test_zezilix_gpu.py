@@ -375,6 +375,9 @@ OTHER = [
     # a recurrence head wider than a warp, equal sizes everywhere
     dict(layers=[oz.wkv_layer(heads=1, dim=40, mlp="dense", ff=40), oz.latent_layer(heads=2, dim=8, rot_dim=8, vdim=8, kv_rank=8, q_rank=8, mlp="moe", experts=4, top=4, expert_ff=8)],
          vocab=80, width=40, streams=2, residual_mult=2.0),
+    # recurrence heads of 80 and 136 channels (token by token also in prompts), keys of 128 + 64 numbers with values of 128, only part of the rotated part turns
+    dict(layers=[oz.wkv_layer(heads=1, dim=80, mlp=None), oz.latent_layer(heads=2, dim=128, rot_dim=64, vdim=128, kv_rank=24, q_rank=16, scale=0.07, rot_dims=40, mlp=None),
+                 oz.wkv_layer(heads=1, dim=136, mlp=None)], vocab=90, width=48, streams=2),
 ]
 
 
