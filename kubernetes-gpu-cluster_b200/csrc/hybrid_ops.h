@@ -245,6 +245,7 @@ struct LatentKvArgs {
   void* k_cache = nullptr; void* v_cache = nullptr;
   int T = 0, H = 0, dim = 0, vdim = 0, block_size = 0;
   int elt = KGE_ELT_BF16;
+  bool vec = false;                        // set by the launcher: every part is a whole number of 16-byte pieces
 };
 int latent_rotary_kvwrite(const LatentKvArgs& a, cudaStream_t st);
 int sigmoid_gate_mul(void* y, int ldy, const void* g, int ldg, int T, int n, int elt, cudaStream_t st);

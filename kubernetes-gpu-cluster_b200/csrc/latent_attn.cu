@@ -32,25 +32,39 @@ __global__ void __launch_bounds__(256) segment_rmsnorm_kernel(SegNormArgs a) {
   }
 }
 
-// the same with four columns per thread; a range of up to 1024 columns stays in registers between the two passes
+// the same with one warp per (token, range) and four columns per load: a range of up to 1024 columns stays in the
+// warp's registers between the sum of squares and the write, and nothing waits on a barrier
 template <typename E>
 __global__ void __launch_bounds__(256) segment_rmsnorm_vec_kernel(SegNormArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float red[33];
-  const int t = blockIdx.x, c = threadIdx.x * 4;
-  for (int g = 0; g < a.nseg; ++g) {
-    const E* x = (const E*)a.x + (int64_t)t * a.ldx + a.col[g];
-    const int n = a.n[g];
-    float v[4] = {0.f, 0.f, 0.f, 0.f}, w[4];
-    if (c < n) ld4(x + c, v);
-    const float ss = fmaf(v[0], v[0], fmaf(v[1], v[1], fmaf(v[2], v[2], v[3] * v[3])));
-    const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)n + a.eps);
+  const int lane = threadIdx.x & 31;
+  const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (item >= (int64_t)a.T * a.nseg) return;
+  const int t = (int)(item / a.nseg), g = (int)(item % a.nseg);
+  const E* x = (const E*)a.x + (int64_t)t * a.ldx + a.col[g];
+  const int n = a.n[g];
+  float v[8][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = (i * 32 + lane) * 4;
     if (c < n) {
+      ld4(x + c, v[i]);
+      ss = fmaf(v[i][0], v[i][0], fmaf(v[i][1], v[i][1], fmaf(v[i][2], v[i][2], fmaf(v[i][3], v[i][3], ss))));
+    }
+  }
+  const float inv = 1.f / sqrtf(warp_sum(ss) / (float)n + a.eps);
+  E* y = (E*)a.out[g] + (int64_t)t * a.ldo[g];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = (i * 32 + lane) * 4;
+    if (c < n) {
+      float w[4];
       ld4((const E*)a.w[g] + c, w);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) w[i] = v[i] * inv * w[i];
-      st4((E*)a.out[g] + (int64_t)t * a.ldo[g] + c, w);
+      for (int k = 0; k < 4; ++k) w[k] = v[i][k] * inv * w[k];
+      st4(y + c, w);
     }
   }
 }
@@ -62,8 +76,9 @@ int segment_rmsnorm(const SegNormArgs& a, cudaStream_t st) {
   for (int g = 0; g < a.nseg; ++g)
     vec = vec && a.n[g] <= 1024 && a.n[g] % 8 == 0 && a.col[g] % 8 == 0 && a.ldo[g] % 8 == 0 && ((reinterpret_cast<uintptr_t>(a.w[g]) | reinterpret_cast<uintptr_t>(a.out[g])) & 15) == 0;
   if (vec) {
-    KGE_CUDA_OK(a.elt == KGE_ELT_F32 ? launch_pdl(segment_rmsnorm_vec_kernel<float>, dim3(a.T), dim3(256), 0, st, a)
-                                     : launch_pdl(segment_rmsnorm_vec_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), 0, st, a));
+    const unsigned blocks = (unsigned)(((int64_t)a.T * a.nseg + 7) / 8);
+    KGE_CUDA_OK(a.elt == KGE_ELT_F32 ? launch_pdl(segment_rmsnorm_vec_kernel<float>, dim3(blocks), dim3(256), 0, st, a)
+                                     : launch_pdl(segment_rmsnorm_vec_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, st, a));
     return 0;
   }
   cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(segment_rmsnorm_kernel<float>, dim3(a.T), dim3(256), 0, st, a)
@@ -115,6 +130,27 @@ __global__ void __launch_bounds__(256) latent_rotary_kvwrite_kernel(LatentKvArgs
   E* vc = (E*)a.v_cache;
   const E* kn = (const E*)a.k_nope + (int64_t)t * a.ldk;
   const E* v = (const E*)a.v + (int64_t)t * a.ldv;
+  constexpr int VE = 16 / (int)sizeof(E);           // elements per 16-byte piece
+  if (a.vec) {
+    // 16-byte pieces: a head's own key part and its value straight from the up-projection, the shared part from shared memory
+    const int kp = a.dim / VE, vp = a.vdim / VE;
+    for (int c = threadIdx.x; c < a.H * kp; c += blockDim.x) {
+      const int h = c / kp, d = (c % kp) * VE;
+      E* dst = kc + ((blk * a.H + h) * a.block_size + off) * a.dim + d;
+      if (d < nope) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(kn + (int64_t)h * nope + d);
+      else {
+        __align__(16) E tmp[VE];
+#pragma unroll
+        for (int i = 0; i < VE; ++i) stf(tmp + i, kr[d - nope + i]);
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(tmp);
+      }
+    }
+    for (int c = threadIdx.x; c < a.H * vp; c += blockDim.x) {
+      const int h = c / vp, d = (c % vp) * VE;
+      *reinterpret_cast<uint4*>(vc + ((blk * a.H + h) * a.block_size + off) * a.vdim + d) = *reinterpret_cast<const uint4*>(v + (int64_t)h * a.vdim + d);
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < a.H * a.dim; c += blockDim.x) {
     const int h = c / a.dim, d = c % a.dim;
     E* dst = kc + ((blk * a.H + h) * a.block_size + off) * a.dim + d;
@@ -131,8 +167,12 @@ int latent_rotary_kvwrite(const LatentKvArgs& a, cudaStream_t st) {
   if (a.T <= 0) return 0;
   KGE_REQUIRE(a.rot_dims % 2 == 0 && a.rot_dims <= a.rot_part && a.rot_part <= a.dim && (a.rot_dims == 0 || a.freq), "latent_rotary_kvwrite: bad rotary sizes");
   const size_t smem = (size_t)(a.rot_dims + a.rot_part) * 4 + 16;
-  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(latent_rotary_kvwrite_kernel<float>, dim3(a.T), dim3(256), smem, st, a)
-                                        : launch_pdl(latent_rotary_kvwrite_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), smem, st, a);
+  LatentKvArgs b = a;
+  const int ve = a.elt == KGE_ELT_F32 ? 4 : 8;
+  b.vec = (a.dim - a.rot_part) % ve == 0 && a.rot_part % ve == 0 && a.vdim % ve == 0 && a.ldk % ve == 0 && a.ldv % ve == 0 &&
+          ((reinterpret_cast<uintptr_t>(a.k_nope) | reinterpret_cast<uintptr_t>(a.v) | reinterpret_cast<uintptr_t>(a.k_cache) | reinterpret_cast<uintptr_t>(a.v_cache)) & 15) == 0;
+  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(latent_rotary_kvwrite_kernel<float>, dim3(a.T), dim3(256), smem, st, b)
+                                        : launch_pdl(latent_rotary_kvwrite_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), smem, st, b);
   KGE_CUDA_OK(ce);
   return 0;
 }
