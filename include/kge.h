@@ -336,7 +336,7 @@ int kge_step(kge_engine* e, const kge_step_batch* batch, int32_t* out_ids_host,
  * 0 gemm (T<=256: weight streaming), 1 gemm (T>256: tensor bound), 2 decode attention,
  * 3 general (prefill / mixed) attention, 4 norms, 5 rope+kv write, 6 activation, 7 embed/gather,
  * 8 sampling, 9 all-reduce.  Timing adds event overhead: never enable it for a headline number. */
-#define KGE_NUM_KERNEL_CATS 13     /* layer-list models add: 10 gated linear recurrence, 11 matrix memory, 12 expert routing + grouped experts */
+#define KGE_NUM_KERNEL_CATS 13     /* layer-list models add: 10 gated linear recurrence, 11 matrix memory (mLSTM, WKV), 12 expert routing + grouped experts */
 typedef struct {
   int64_t launches;
   double ms;          /* summed device time of the launches            */

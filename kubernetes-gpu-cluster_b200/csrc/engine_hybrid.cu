@@ -1,7 +1,8 @@
 // Layer-list ("hybrid") models in the engine: a config.json that lists its layers, each with a token mixer (gated
-// linear recurrence, attention and a matrix memory side by side, or attention alone with rotary positions, a soft cap
-// and sink logits) and a feed-forward (dense or mixture of experts), reading ONE norm of an fp32 residual stream or a
-// norm each in sequence.  This file loads such a model (weights in the engine's storage
+// linear recurrence, attention and a matrix memory side by side, attention alone with rotary positions, a soft cap
+// and sink logits, a WKV recurrence, or attention through latents) and a feed-forward (dense or mixture of experts),
+// reading ONE norm of an fp32 residual stream, a norm each in sequence, or a norm each of a hyper-connected residual
+// (several copies of the stream).  This file loads such a model (weights in the engine's storage
 // type, fused where one activation feeds several projections), sizes its arena, paged caches and recurrent-state pool,
 // and runs its step: the same flattened batch, block tables and slot mapping as every other model, plus a state slot
 // per request.  Nothing here depends on how a prompt was cut into steps: recurrences continue from the slot, attention

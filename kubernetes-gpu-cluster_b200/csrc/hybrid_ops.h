@@ -1,6 +1,8 @@
 // Launchers of the kernels that layer-list ("hybrid") models add to the library: a shape-agnostic linear layer with
 // grouped / gathered rows, fp32-residual norms, biased chunk-masked paged attention (soft cap, sink logits), rotary
-// positions with a whole-projection norm, the gated linear recurrence (RG-LRU), the matrix memory (mLSTM) and the mixture-of-experts router.  Every mechanism takes its sizes and constants
+// positions with a whole-projection norm, the gated linear recurrence (RG-LRU), the matrix memory (mLSTM), the
+// mixture-of-experts router, the hyper-connected residual (several streams), the WKV recurrence and the row-wise parts of
+// attention through latents.  Every mechanism takes its sizes and constants
 // as arguments.  `elt` names the storage type of activations and weights: KGE_ELT_BF16 or KGE_ELT_F32; what the
 // mechanisms compute in 32 bits (softmax, norms, routers, residual sums, recurrent state and everything that enters a
 // recurrence besides projections and short convolutions) is 32-bit in both.
