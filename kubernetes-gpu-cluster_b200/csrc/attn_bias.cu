@@ -10,6 +10,23 @@ namespace kge {
 
 constexpr int ATT_WARPS = 4, ATT_MAXV = 8;   // value columns per lane: vdim <= 32 * ATT_MAXV
 
+// Keys of a row with a window: first the `prefix` keys - kept first tokens that have left the window (their own rows of
+// the caches) or pooled blocks that lie wholly before it (rows of the pooled caches) - then the window's tokens.
+__device__ __forceinline__ int prefix_keys(const AttnBiasArgs& a, int i) {
+  if (a.window <= 0 || i < a.window) return 0;
+  const int before = i - a.window + 1;              // positions 0 .. before - 1 have left the window
+  return a.pool > 0 ? before / a.pool : min(a.keep_first, before);
+}
+__device__ __forceinline__ int window_lo(const AttnBiasArgs& a, int i) {
+  const int lo = a.chunk > 0 ? (i / a.chunk) * a.chunk : 0;
+  return a.window > 0 ? max(lo, i - a.window + 1) : lo;
+}
+// the cache row of prefix key u of a request (pooled caches when pool > 0)
+__device__ __forceinline__ int64_t prefix_row(const AttnBiasArgs& a, const int32_t* bt, int g, int u) {
+  if (a.pool > 0) return ((int64_t)bt[u / a.pool_slots] * a.G + g) * a.pool_slots + u % a.pool_slots;
+  return ((int64_t)bt[u / a.block_size] * a.G + g) * a.block_size + u % a.block_size;
+}
+
 template <typename E>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attn_bias_chunk_kernel(AttnBiasArgs a) {
   pdl_launch_dependents();
@@ -24,28 +41,34 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_bias_chunk_kernel(AttnBia
   for (int d = lane; d < a.dim; d += 32) qs[d] = ldf(q + d);
   __syncwarp();
   const int b = a.token_req[t], i = a.positions[t];
-  const int lo = a.chunk > 0 ? (i / a.chunk) * a.chunk : 0;
+  const int lo = window_lo(a, i), npre = prefix_keys(a, i);
   const int g = h / (a.H / a.G);
   const float slope = a.bias_span > 0.f ? exp2f(-a.bias_span * (float)(h + 1) / (float)a.H) : 0.f;
   const int32_t* bt = a.block_table + (int64_t)b * a.max_blocks;
   const E* kc = (const E*)a.k_cache;
   const E* vc = (const E*)a.v_cache;
+  const bool pooled = a.pool > 0;
+  const E* pkc = pooled ? (const E*)a.pk_cache : kc;
+  const E* pvc = pooled ? (const E*)a.pv_cache : vc;
   float m = -INFINITY, l = 0.f, o[ATT_MAXV];
 #pragma unroll
   for (int c = 0; c < ATT_MAXV; ++c) o[c] = 0.f;
-  for (int j0 = lo; j0 <= i; j0 += 32) {
-    const int j = j0 + lane;
-    const bool valid = j <= i;
+  // the row's keys in one list: npre prefix keys, then positions lo .. i
+  const int nkeys = npre + (i - lo + 1);
+  for (int u0 = 0; u0 < nkeys; u0 += 32) {
+    const int u = u0 + lane;
+    const bool valid = u < nkeys, pre = u < npre;
+    const int j = lo + (u - npre);
     int64_t row = 0;
     float s = -INFINITY;
     if (valid) {
-      row = ((int64_t)bt[j / a.block_size] * a.G + g) * a.block_size + j % a.block_size;
-      const E* kr = kc + row * a.dim;
+      row = pre ? prefix_row(a, bt, g, u) : ((int64_t)bt[j / a.block_size] * a.G + g) * a.block_size + j % a.block_size;
+      const E* kr = (pre ? pkc : kc) + row * a.dim;
       float acc = 0.f;
       for (int d = 0; d < a.dim; ++d) acc = fmaf(qs[d], ldf(kr + d), acc);
       acc *= a.scale;
       if (a.softcap > 0.f) acc = a.softcap * tanhf(acc / a.softcap);
-      s = acc - slope * (float)(i - j);
+      s = pre ? acc : acc - slope * (float)(i - j);
     }
     const float mn = fmaxf(m, warp_max(s));
     const float p = valid ? expf(s - mn) : 0.f;
@@ -54,11 +77,11 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_bias_chunk_kernel(AttnBia
     m = mn;
 #pragma unroll
     for (int c = 0; c < ATT_MAXV; ++c) o[c] *= corr;
-    const int cnt = min(32, i - j0 + 1);
+    const int cnt = min(32, nkeys - u0);
     for (int jj = 0; jj < cnt; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const int64_t rj = __shfl_sync(0xffffffffu, row, jj);
-      const E* vr = vc + rj * a.vdim;
+      const E* vr = (u0 + jj < npre ? pvc : vc) + rj * a.vdim;
 #pragma unroll
       for (int c = 0; c < ATT_MAXV; ++c) {
         const int col = c * 32 + lane;
@@ -127,7 +150,7 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
   E* Ks = reinterpret_cast<E*>(am_smem + (ROWS ? 0 : warp) * region);
   E* Vs = Ks + AM_KT * kst;
   // this thread's two rows: qr and qr + 8 of the tile
-  int pos[2], lo[2], tok[2], head[2];
+  int pos[2], lo[2], tok[2], head[2], npre[2];
   float slope2[2];
   const float log2e = 1.4426950408889634f;
 #pragma unroll
@@ -137,18 +160,21 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
     tok[h] = rs + (valid ? r : nrows - 1) / hpg;
     head[h] = g * hpg + (valid ? r : nrows - 1) % hpg;
     pos[h] = valid ? a.positions[tok[h]] : -1;                       // -1: no key is visible, the row is never written
-    lo[h] = (a.chunk > 0 && pos[h] >= 0) ? (pos[h] / a.chunk) * a.chunk : 0;
+    lo[h] = pos[h] >= 0 ? window_lo(a, pos[h]) : 0;
+    npre[h] = pos[h] >= 0 ? prefix_keys(a, pos[h]) : 0;
     slope2[h] = a.bias_span > 0.f ? exp2f(-a.bias_span * (float)(head[h] + 1) / (float)a.H) * log2e : 0.f;
   }
   const int pos_first = a.positions[rs + Rc / hpg], pos_last = a.positions[rs + min(Rc + (ROWS ? 16 * AM_WARPS : 16) - 1, nrows - 1) / hpg];
-  const int lo_min = a.chunk > 0 ? (pos_first / a.chunk) * a.chunk : 0;
-  const int ntiles = (pos_last - lo_min + AM_KT) / AM_KT;
+  const int lo_min = window_lo(a, pos_first);
+  // prefix keys (kept first tokens or pooled blocks) come first, in tiles of their own; the last row of the CTA sees the most
+  const int pre_cta = prefix_keys(a, pos_last), ptiles = (pre_cta + AM_KT - 1) / AM_KT;
+  const int ntiles = ptiles + (pos_last - lo_min + AM_KT) / AM_KT;
   // the keys this warp's own rows can see (ROWS: tiles outside are staged for the others but not computed here)
   // (the same for every lane of the warp: the mma instructions below need all 32 lanes on one path)
   const bool wany = R0 < nrows;
   const int own_hi = wany ? a.positions[rs + min(R0 + 15, nrows - 1) / hpg] : -1;
   const int own_first = wany ? a.positions[rs + R0 / hpg] : 0;
-  const int own_lo = a.chunk > 0 ? (own_first / a.chunk) * a.chunk : 0;
+  const int own_lo = window_lo(a, own_first), own_pre = wany ? prefix_keys(a, own_hi) : 0;
   const float scale2 = a.scale * log2e;
   const float cap2 = a.softcap * log2e, cap_in = a.softcap > 0.f ? a.scale / a.softcap : 0.f;   // capped scores, in units of log 2
   uint32_t qf[AM_MAXD / 16][4];
@@ -170,15 +196,18 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
   for (int v = 0; v < AM_MAXD / 8; ++v) o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   const int32_t* bt = a.block_table + (int64_t)b * a.max_blocks;
-  const E* kc = (const E*)a.k_cache;
-  const E* vc = (const E*)a.v_cache;
   const int kseg = dim >> 3, vseg = vdim >> 3;
   for (int kt = ROWS ? 0 : warp; kt < ntiles; kt += ROWS ? 1 : AM_WARPS) {
-    const int j0 = lo_min + kt * AM_KT;
+    const bool ptile = kt < ptiles;                         // a tile of prefix keys: j0 counts them from 0
+    const int j0 = ptile ? kt * AM_KT : lo_min + (kt - ptiles) * AM_KT;
+    const E* kc = (const E*)(ptile && a.pool > 0 ? a.pk_cache : a.k_cache);
+    const E* vc = (const E*)(ptile && a.pool > 0 ? a.pv_cache : a.v_cache);
     if (ROWS) __syncthreads();                              // the previous tile has been read by every warp
     // stage the tile: lane i knows where key j0 + i lives; the 16-byte pieces of a row are fetched by consecutive lanes
     const int jl = j0 + lane;
-    const int64_t myrow = jl <= pos_last ? ((int64_t)bt[jl / a.block_size] * a.G + g) * a.block_size + jl % a.block_size : -1;
+    int64_t myrow = -1;
+    if (ptile) { if (jl < pre_cta) myrow = prefix_row(a, bt, g, jl); }
+    else if (jl <= pos_last) myrow = ((int64_t)bt[jl / a.block_size] * a.G + g) * a.block_size + jl % a.block_size;
     const int sid = ROWS ? threadIdx.x : lane, sstep = ROWS ? AM_WARPS * 32 : 32;
     // four 16-byte pieces are requested before the first is stored, so a tile costs a few memory round trips, not one
     // per piece (whole warps run the loops: the shuffle needs every lane)
@@ -211,7 +240,7 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
       for (int u = 0; u < 4; ++u) *reinterpret_cast<uint4*>(Vs + dst[u]) = v[u];
     }
     if (ROWS) __syncthreads(); else __syncwarp();
-    if (ROWS && (j0 > own_hi || j0 + AM_KT <= own_lo)) continue;
+    if (ROWS && (ptile ? j0 >= own_pre : (j0 > own_hi || j0 + AM_KT <= own_lo))) continue;
     float sacc[4][4];
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
@@ -232,10 +261,10 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int h = c >> 1, j = j0 + nt * 8 + qc + (c & 1);
-        const bool vis = j <= pos[h] && j >= lo[h];
+        const bool vis = ptile ? j < npre[h] : (j <= pos[h] && j >= lo[h]);
         float sc = sacc[nt][c] * scale2;
         if (cap2 > 0.f) sc = cap2 * tanh_fast(sacc[nt][c] * cap_in);
-        const float sv = vis ? sc - slope2[h] * (float)(pos[h] - j) : -INFINITY;
+        const float sv = vis ? (ptile ? sc : sc - slope2[h] * (float)(pos[h] - j)) : -INFINITY;
         sacc[nt][c] = sv;
         tmax[h] = fmaxf(tmax[h], sv);
       }
@@ -347,6 +376,9 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
 
 int attn_bias_chunk(const AttnBiasArgs& a, cudaStream_t st) {
   if (a.T <= 0) return 0;
+  KGE_REQUIRE(a.window >= 0 && (a.window > 0 || (a.keep_first == 0 && a.pool == 0)) && !(a.keep_first > 0 && a.pool > 0) && (a.window == 0 || a.bias_span == 0.f) &&
+              (a.pool == 0 || (a.pk_cache && a.pv_cache && a.pool_slots > 0)),
+              "attn_bias_chunk: window %d with %d kept tokens / pooled blocks of %d", a.window, a.keep_first, a.pool);
   if (a.elt == KGE_ELT_BF16 && a.max_q > 0 && a.dim % 16 == 0 && a.dim <= AM_MAXD && a.vdim % 8 == 0 && a.vdim <= AM_MAXD && a.ldq % 2 == 0 &&
       a.H % a.G == 0 && (reinterpret_cast<uintptr_t>(a.q) & 3) == 0 && a.B <= 65535 && a.G <= 65535) {
     const int hpg = a.H / a.G;
@@ -405,6 +437,39 @@ int kv_write_any(const void* k, int ldk, const void* v, int ldv, const int64_t* 
       ? launch_pdl(kv_write_any_kernel<float>, dim3(T), dim3(128), 0, st, (const float*)k, ldk, (const float*)v, ldv, slots, (float*)k_cache, (float*)v_cache, G, dim, vdim, block_size)
       : launch_pdl(kv_write_any_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, st, (const __nv_bfloat16*)k, ldk, (const __nv_bfloat16*)v, ldv, slots,
                    (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, G, dim, vdim, block_size);
+  KGE_CUDA_OK(ce);
+  return 0;
+}
+
+// One block per token; only a token that ends a block of `pool` positions has work: the block's keys and values are read
+// back from the caches (so what is averaged is what the attention reads), summed in fp32 in ascending position and
+// divided by the count.
+template <typename E>
+__global__ void __launch_bounds__(128) pool_kv_write_kernel(PoolKvArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, pos = a.positions[t];
+  if ((pos + 1) % a.pool != 0) return;
+  const int pb = pos / a.pool, p0 = pb * a.pool;
+  const int32_t* bt = a.block_table + (int64_t)a.token_req[t] * a.max_blocks;
+  const int64_t dblk = bt[pb / a.pool_slots], doff = pb % a.pool_slots;
+  const int nk = a.G * a.dim, nv = a.G * a.vdim;
+  for (int c = threadIdx.x; c < nk + nv; c += blockDim.x) {
+    const bool isk = c < nk;
+    const int cc = isk ? c : c - nk, w = isk ? a.dim : a.vdim, g = cc / w, dd = cc % w;
+    const E* src = (const E*)(isk ? a.k_cache : a.v_cache);
+    float acc = 0.f;
+    for (int j = p0; j <= pos; ++j) acc += ldf(src + (((int64_t)bt[j / a.block_size] * a.G + g) * a.block_size + j % a.block_size) * w + dd);
+    E* dst = (E*)(isk ? a.pk_cache : a.pv_cache);
+    stf(dst + ((dblk * a.G + g) * a.pool_slots + doff) * w + dd, acc / (float)a.pool);
+  }
+}
+
+int pool_kv_write(const PoolKvArgs& a, cudaStream_t st) {
+  if (a.T <= 0) return 0;
+  KGE_REQUIRE(a.pool >= 1 && a.pool_slots >= 1 && a.pool_slots * a.pool >= a.block_size, "pool_kv_write: blocks of %d positions, %d entries per page of %d", a.pool, a.pool_slots, a.block_size);
+  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(pool_kv_write_kernel<float>, dim3(a.T), dim3(128), 0, st, a)
+                                        : launch_pdl(pool_kv_write_kernel<__nv_bfloat16>, dim3(a.T), dim3(128), 0, st, a);
   KGE_CUDA_OK(ce);
   return 0;
 }

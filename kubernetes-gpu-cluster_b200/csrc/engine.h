@@ -90,6 +90,19 @@ struct HybridLayerW {
   int lat_dkv = 0, lat_g = 0;
   // dense clamped gated unit: [gate | up] rows in one block (`up` names the second half)
   void* ff_gate = nullptr;
+  void* ff_gate_b = nullptr;                  // [gate.b | up.b] of a gated unit whose projections carry biases
+  // norms of a sublayer's result (models that norm before AND after a sublayer)
+  void *norm1b = nullptr, *norm2b = nullptr;
+  // windowed attention beside gated linear attention: `proj` holds [q | k | v | mq | mk | mv | mg | a1] (offsets off_*,
+  // off_a1), conv_w the three convolutions stacked [q | k | v channels, taps], q_norm / k_norm the per-head weights,
+  // rot_freq / v_freq the rotary frequencies of q / k and of the values (double), `o` / `o2` the two output projections,
+  // side_norm the RMS-norm weights of the two sides' outputs, wkv_w2 the decay's second projection (with its bias),
+  // wkv_norm the per-head output norm repeated for every head.  Windowed attention over pooled blocks: `proj` holds
+  // [q | k | v] with biases, `o` carries a bias, pkc / pvc are the pooled caches.
+  int off_a1 = 0;
+  double* v_freq = nullptr;
+  void* side_norm[2] = {nullptr, nullptr};
+  void *pkc = nullptr, *pvc = nullptr;
   // hyper-connected residual, per sublayer (0: mixer, 1: feed-forward), fp32 on the device: read weights [S], write
   // weights [S], mix matrix [S, S] (from, to), and the per-column scale of the sublayer's result [d]; null = ones / identity
   float *hc_in[2] = {nullptr, nullptr}, *hc_out[2] = {nullptr, nullptr}, *hc_mix[2] = {nullptr, nullptr}, *col_scale[2] = {nullptr, nullptr};
@@ -121,6 +134,7 @@ struct kge_engine {
   void *mixes = nullptr, *rkvg = nullptr;    // WKV: the blended inputs [5, tokens, d] and the projections [4, tokens, heads * dim]
   void *latq = nullptr, *latc = nullptr, *latkv = nullptr, *qbuf = nullptr;   // latent attention: normed latents, [k | v] up-projections, queries
   void *hx = nullptr, *pbuf = nullptr, *ubuf = nullptr, *mixbuf = nullptr, *obuf1 = nullptr, *obuf2 = nullptr, *ffbuf = nullptr;
+  void* mixbuf2 = nullptr;                   // the second side of a mixer whose two sides have output projections of their own
   void *moe_hidden = nullptr, *moe_out = nullptr, *hsel = nullptr, *moe_xperm = nullptr, *moe_operm = nullptr;
   int32_t* moe_tile_group = nullptr;         // expert of every 256-row tile of the padded routed rows (prompt steps)
   int64_t moe_rows_padded = 0;               // rows the routed-row buffers hold

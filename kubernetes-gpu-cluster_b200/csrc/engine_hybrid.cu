@@ -1,8 +1,9 @@
 // Layer-list ("hybrid") models in the engine: a config.json that lists its layers, each with a token mixer (gated
 // linear recurrence, attention and a matrix memory side by side, attention alone with rotary positions, a soft cap
-// and sink logits, a WKV recurrence, or attention through latents) and a feed-forward (dense or mixture of experts),
-// reading ONE norm of an fp32 residual stream, a norm each in sequence, or a norm each of a hyper-connected residual
-// (several copies of the stream).  This file loads such a model (weights in the engine's storage
+// and sink logits, a WKV recurrence, attention through latents, windowed attention with kept first tokens beside gated
+// linear attention, or windowed attention over pooled blocks) and a feed-forward (dense or mixture of experts),
+// reading ONE norm of an fp32 residual stream, a norm each in sequence (optionally with a norm of each result as
+// well), or a norm each of a hyper-connected residual (several copies of the stream).  This file loads such a model (weights in the engine's storage
 // type, fused where one activation feeds several projections), sizes its arena, paged caches and recurrent-state pool,
 // and runs its step: the same flattened batch, block tables and slot mapping as every other model, plus a state slot
 // per request.  Nothing here depends on how a prompt was cut into steps: recurrences continue from the slot, attention
@@ -140,7 +141,7 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
 #define HB_OK(p) do { if (!(p)) return fail(b.err); } while (0)
   HB_OK(e->embed = (bf16*)b.mat({"embed"}, {s.vocab}, d, ws));
   HB_OK(e->lm_head = (bf16*)b.mat({"head"}, {s.vocab}, d, ws));
-  const bool plain_norm_w = s.hyb_layernorm || s.streams > 0;      // the norm weight multiplies as it is (else it is applied as 1 + w)
+  const bool plain_norm_w = s.hyb_layernorm || s.streams > 0 || s.hyb_postnorm;      // the norm weight multiplies as it is (else it is applied as 1 + w)
   HB_OK(e->final_w = (bf16*)b.mat({"final.norm"}, {d}, 1, 0.f, plain_norm_w ? 1.f : 0.f));
   if (s.embed_norm) HB_OK(e->embed_norm_w = b.mat({"embed.norm"}, {d}, 1, 0.f, 1.f));
   e->hyb.resize(s.L);
@@ -148,22 +149,29 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   int max_mo = 1;
   int max_proj = 1, max_mix = 1, max_ff = 1, max_gate = 1, max_u = 1, max_top = 0, max_eff = 1, max_E = 1;
   int max_hd = 0, max_qr = 0, max_kvr = 0, max_lkv = 0, max_lq = 0;      // WKV heads * dim; latent ranks, [k | v] and query widths
+  int max_mix2 = 0;
   for (int i = 0; i < s.L; ++i) {
     const HybridLayerSpec& h = s.hybrid[i];
     HybridLayerW& L = e->hyb[i];
     const std::string p = "l" + std::to_string(h.tensor_index >= 0 ? h.tensor_index : i) + ".", mx = p + "mix.", fp = p + "mlp.";
     if (h.weights_of >= 0) {                   // another layer's tensors; the paged caches below and the state stay this layer's own
       L = e->hyb[h.weights_of];
-      L.kc = L.vc = nullptr;
+      L.kc = L.vc = L.pkc = L.pvc = nullptr;
       L.state_off = state_floats;
       if (h.mixer == HybridLayerSpec::RGLRU) state_floats += rglru_state_floats(h.width, h.conv);
       else if (h.mixer == HybridLayerSpec::PARALLEL) state_floats += mlstm_state_floats(h.m_heads, h.m_dim, h.m_vdim);
       else if (h.mixer == HybridLayerSpec::WKV) state_floats += wkv_state_floats(d, h.heads, h.dim);
+      else if (h.mixer == HybridLayerSpec::WINDOW_GLA)
+        state_floats += short_conv_state_floats((h.heads + h.kv_heads) * h.dim + h.kv_heads * h.vdim, h.conv) + gla_state_floats(h.m_heads, h.m_dim, h.m_vdim);
       continue;
     }
     const float norm_one = plain_norm_w ? 1.f : 0.f;      // the weight that leaves the normed row as it is
     HB_OK(L.norm1 = b.mat({p + "norm1"}, {d}, 1, 0.f, norm_one));
     if (s.hyb_prenorm_pair && h.mlp != HybridLayerSpec::NONE) HB_OK(L.norm2 = b.mat({p + "norm2"}, {d}, 1, 0.f, norm_one));
+    if (s.hyb_postnorm) {
+      HB_OK(L.norm1b = b.mat({p + "norm1b"}, {d}, 1, 0.f, 1.f));
+      if (h.mlp != HybridLayerSpec::NONE) HB_OK(L.norm2b = b.mat({p + "norm2b"}, {d}, 1, 0.f, 1.f));
+    }
     L.state_off = state_floats;
     if (h.mixer == HybridLayerSpec::RGLRU) {
       const int w = h.width, bw = w / h.blocks;
@@ -200,6 +208,67 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
       L.o.N = d; L.o.K = h.heads * h.vdim;
       HB_OK(L.o.w = b.mat({mx + "o"}, {d}, h.heads * h.vdim, ws));
       max_proj = std::max(max_proj, L.qk.N); max_mix = std::max(max_mix, L.o.K);
+    } else if (h.mixer == HybridLayerSpec::WINDOW_GLA) {
+      const int nq = h.heads * h.dim, nk = h.kv_heads * h.dim, nv = h.kv_heads * h.vdim, mk = h.m_heads * h.m_dim, mv = h.m_heads * h.m_vdim;
+      const std::string a = mx + "left.", r = mx + "right.";
+      int lr = h.decay_rank;
+      if (!b.dummy()) {
+        const HostTensor* t1 = md.find(r + "a1");
+        if (!t1 || t1->shape.size() != 2) return fail("missing tensor " + r + "a1");
+        lr = (int)t1->shape[0];
+      } else if (lr <= 0) lr = 16;
+      L.off_k = nq; L.off_v = nq + nk; L.off_mq = L.off_v + nv; L.off_mk = L.off_mq + mk; L.off_mv = L.off_mk + mk; L.off_mg = L.off_mv + mv; L.off_a1 = L.off_mg + mv;
+      L.proj.N = L.off_a1 + lr; L.proj.K = d;
+      HB_OK(L.proj.w = b.mat({a + "q", a + "k", a + "v", r + "q", r + "k", r + "v", r + "g", r + "a1"}, {nq, nk, nv, mk, mk, mv, mv, lr}, d, ws));
+      if (b.dummy()) HB_OK(L.proj.b = b.mat({}, {L.proj.N}, 1, 0.f, 0.f));
+      else {
+        std::vector<float> bias;      // the attention side's projections carry biases, the other side's do not
+        if (!b.stack({a + "q.b", a + "k.b", a + "v.b"}, {nq, nk, nv}, 1, &bias)) return fail(b.err);
+        bias.resize((size_t)L.proj.N, 0.f);
+        HB_OK(L.proj.b = b.upload(bias));
+      }
+      HB_OK(L.conv_w = b.mat({a + "q.conv", a + "k.conv", a + "v.conv"}, {nq, nk, nv}, h.conv, 0.5f));
+      HB_OK(L.q_norm = b.mat({a + "q.norm"}, {h.dim}, 1, 0.f, 1.f));
+      HB_OK(L.k_norm = b.mat({a + "k.norm"}, {h.dim}, 1, 0.f, 1.f));
+      if (h.rot_dims > 0) {
+        std::vector<double> fr((size_t)h.rot_dims / 2);
+        rotary_frequencies(h.rot_dims, h.rot_base, 0.0, 0.0, 32.0, 1.0, fr.data(), &L.rot_mult);
+        HB_OK(L.rot_freq = b.upload_raw(fr));
+      }
+      if (h.v_rot) {
+        std::vector<double> fr((size_t)h.vdim / 2);
+        float one;
+        rotary_frequencies(h.vdim, h.rot_base, 0.0, 0.0, 32.0, 1.0, fr.data(), &one);
+        HB_OK(L.v_freq = b.upload_raw(fr));
+      }
+      L.o.N = d; L.o.K = h.heads * h.vdim;
+      HB_OK(L.o.w = b.mat({a + "o"}, {d}, L.o.K, ws));
+      L.o2.N = d; L.o2.K = mv;
+      HB_OK(L.o2.w = b.mat({r + "o"}, {d}, mv, ws));
+      L.wkv_w2.N = mk; L.wkv_w2.K = lr;
+      HB_OK(L.wkv_w2.w = b.mat({r + "a2"}, {mk}, lr, ws));
+      HB_OK(L.wkv_w2.b = b.mat({r + "a2.b"}, {mk}, 1, 0.f, 2.f));
+      {
+        // the per-head norm of the read-out: one weight of m_vdim numbers, laid out once per head
+        std::vector<std::string> rep((size_t)h.m_heads, r + "norm");
+        std::vector<int64_t> lead((size_t)h.m_heads, h.m_vdim);
+        HB_OK(L.wkv_norm = b.mat(rep, lead, 1, 0.f, 1.f));
+      }
+      HB_OK(L.side_norm[0] = b.mat({a + "out"}, {d}, 1, 0.f, 1.f));
+      HB_OK(L.side_norm[1] = b.mat({r + "out"}, {d}, 1, 0.f, 1.f));
+      state_floats += short_conv_state_floats(nq + nk + nv, h.conv) + gla_state_floats(h.m_heads, h.m_dim, h.m_vdim);
+      max_proj = std::max(max_proj, L.proj.N); max_u = std::max(max_u, nq + nk + nv); max_mix = std::max(max_mix, L.o.K); max_mix2 = std::max(max_mix2, mv);
+      max_gate = std::max(max_gate, mk); max_mo = std::max(max_mo, mv);
+    } else if (h.mixer == HybridLayerSpec::POOLED) {
+      const int nq = h.heads * h.dim, nk = h.kv_heads * h.dim, nv = h.kv_heads * h.vdim;
+      L.off_k = nq; L.off_v = nq + nk;
+      L.proj.N = nq + nk + nv; L.proj.K = d;
+      HB_OK(L.proj.w = b.mat({mx + "q", mx + "k", mx + "v"}, {nq, nk, nv}, d, ws));
+      HB_OK(L.proj.b = b.mat({mx + "q.b", mx + "k.b", mx + "v.b"}, {nq, nk, nv}, 1, 0.f, 0.f));
+      L.o.N = d; L.o.K = h.heads * h.vdim;
+      HB_OK(L.o.w = b.mat({mx + "o"}, {d}, L.o.K, ws));
+      HB_OK(L.o.b = b.mat({mx + "o.b"}, {d}, 1, 0.f, 0.f));
+      max_proj = std::max(max_proj, L.proj.N); max_mix = std::max(max_mix, L.o.K);
     } else if (h.mixer == HybridLayerSpec::WKV) {
       const int hd = h.heads * h.dim;
       int lr = h.decay_rank;
@@ -288,7 +357,16 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
         if (bad || !b.err.empty()) return fail(b.err);
       }
     }
-    if (h.mlp == HybridLayerSpec::DENSE && h.ff_limit > 0.f) {
+    if (h.mlp == HybridLayerSpec::DENSE && h.ff_silu_bias) {
+      // silu(gate h + b) * (up h + b), then down with its bias: [gate | up] rows and biases in one block
+      L.up.N = 2 * h.ff; L.up.K = d; L.down.N = d; L.down.K = h.ff;
+      HB_OK(L.ff_gate = b.mat({fp + "gate", fp + "up"}, {h.ff, h.ff}, d, ws));
+      HB_OK(L.ff_gate_b = b.mat({fp + "gate.b", fp + "up.b"}, {h.ff, h.ff}, 1, 0.f, 0.f));
+      L.up.w = L.ff_gate; L.up.b = L.ff_gate_b;
+      HB_OK(L.down.w = b.mat({fp + "down"}, {d}, h.ff, ws));
+      HB_OK(L.down.b = b.mat({fp + "down.b"}, {d}, 1, 0.f, 0.f));
+      max_ff = std::max(max_ff, 3 * h.ff);
+    } else if (h.mlp == HybridLayerSpec::DENSE && h.ff_limit > 0.f) {
       L.up.N = h.ff; L.up.K = d; L.down.N = d; L.down.K = h.ff;
       HB_OK(L.ff_gate = b.mat({fp + "gate", fp + "up"}, {h.ff, h.ff}, d, ws));
       L.up.w = (uint8_t*)L.ff_gate + (int64_t)h.ff * d * b.esz();
@@ -352,6 +430,7 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   e->pbuf = aalloc((int64_t)Tm * max_proj, es);
   e->ubuf = aalloc((int64_t)Tm * max_u, es);
   e->mixbuf = aalloc((int64_t)Tm * max_mix, es);
+  if (max_mix2 > 0) { e->mixbuf2 = aalloc((int64_t)Tm * max_mix2, es); if (!e->mixbuf2) return fail(b.err); }
   e->obuf1 = aalloc((int64_t)Tm * d, es);
   e->obuf2 = aalloc((int64_t)Tm * d, es);
   e->ffbuf = aalloc((int64_t)Tm * max_ff, es);
@@ -414,7 +493,7 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
   // paged caches of the attention sides: K [blocks, G, block_size, dim], V [blocks, G, block_size, vdim] per layer
   int64_t blk_bytes = 0;
   for (auto& h : s.hybrid)
-    if (h.has_cache()) blk_bytes += (int64_t)h.kv_heads * e->cfg.block_size * (h.dim + h.vdim) * es;
+    if (h.has_cache()) blk_bytes += (int64_t)h.kv_heads * (e->cfg.block_size + (h.pool > 0 ? pool_slots_per_block(e->cfg.block_size, h.pool) : 0)) * (h.dim + h.vdim) * es;
   int nb = e->cfg.num_blocks;
   if (nb <= 0) {
     const int64_t cap = (int64_t)e->cfg.max_num_seqs * e->max_blocks_per_seq + 1;
@@ -441,6 +520,15 @@ int hybrid_engine_build(kge_engine* e, const ModelDir& md, int64_t dummy_seed, s
     if (!e->hyb[i].kc || !e->hyb[i].vc) return fail("KV pool allocation failed");
     cudaMemsetAsync(e->hyb[i].kc, 0, (size_t)nk * es, e->stream);
     cudaMemsetAsync(e->hyb[i].vc, 0, (size_t)nv * es, e->stream);
+    if (h.pool > 0) {
+      // one pooled key / value per block of `pool` positions, on the same pages: entry b of a request lives in its page b / slots
+      const int ps = pool_slots_per_block(e->cfg.block_size, h.pool);
+      const int64_t pk = (int64_t)nb * h.kv_heads * ps * h.dim, pv = (int64_t)nb * h.kv_heads * ps * h.vdim;
+      e->hyb[i].pkc = aalloc(pk, es); e->hyb[i].pvc = aalloc(pv, es);
+      if (!e->hyb[i].pkc || !e->hyb[i].pvc) return fail("pooled KV pool allocation failed");
+      cudaMemsetAsync(e->hyb[i].pkc, 0, (size_t)pk * es, e->stream);
+      cudaMemsetAsync(e->hyb[i].pvc, 0, (size_t)pv * es, e->stream);
+    }
   }
   SchedConfig sc;
   sc.max_num_seqs = e->cfg.max_num_seqs;
@@ -508,6 +596,7 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
   struct PdlOff { bool on; explicit PdlOff(bool o) : on(o) { if (on) pdl_suspend(true); } ~PdlOff() { if (on) pdl_suspend(false); } } pdl_off(!decode_only);
   // the model's norm of residual rows: RMS with the weight applied as 1 + w, or the weight-only layer norm
   auto layer_norm = [&](void* y, const int32_t* rows, const void* w, int R, float out_scale) -> int {
+    if (s.hyb_postnorm) return group_rmsnorm_f32in(y, e->res32, rows, w, R, d, s.norm_groups, s.eps, out_scale, elt, st);
     return s.hyb_layernorm ? layernorm_f32in(y, e->res32, rows, w, R, d, s.eps, out_scale, elt, st)
                            : rmsnorm_f32in(y, e->res32, rows, w, R, d, s.eps, 1.f, out_scale, elt, st);
   };
@@ -527,8 +616,10 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
     const HybridLayerSpec& h = s.hybrid[i];
     const HybridLayerW& L = e->hyb[i];
     if (hyper) { if (!hx_ready) HFWD(C_NORM, Td * (4.0 * S + es), 0, stream_read(e->hx, L.hc_in[0], nullptr, L.norm1, T, 1.f, nullptr)); hx_ready = false; }
-    else HFWD(C_NORM, Td * (4 + es), 0, layer_norm(e->hx, nullptr, L.norm1, T, 1.f));
+    else if (!hx_ready) HFWD(C_NORM, Td * (4 + es), 0, layer_norm(e->hx, nullptr, L.norm1, T, 1.f));
+    hx_ready = false;
     CombineArgs cb;
+    const void* inner_w[2] = {nullptr, nullptr};      // a norm of a source's own before the sources are summed (models with normed results)
     bool y32_used = false;
     int sub = 0;                                       // the sublayer whose result is being summed (0: mixer, 1: feed-forward)
     auto add_src = [&](const void* p, int ld, float scale, const float* rscale = nullptr, int rs_stride = 0) {
@@ -548,6 +639,17 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
     };
     // the write of the streams also forms the next sublayer's normed input (the feed-forward's, or the next layer's mixer's)
     auto flush = [&]() -> int {
+      if (s.hyb_postnorm) {
+        // the sublayer's result through its own norm into the stream, and the next sublayer's normed input in the same pass
+        PostNormArgs pa;
+        pa.res = e->res32; pa.nsrc = cb.n; pa.src_scale = cb.scale[0]; pa.T = T; pa.d = d; pa.groups = s.norm_groups; pa.eps = s.eps; pa.elt = elt;
+        for (int q = 0; q < cb.n && q < 2; ++q) { pa.src[q] = cb.src[q]; pa.ld[q] = cb.ld[q]; pa.inner_w[q] = inner_w[q]; }
+        pa.post_w = sub == 0 ? L.norm1b : L.norm2b;
+        if (sub == 0 && h.mlp != HybridLayerSpec::NONE) { pa.next_w = L.norm2; pa.next_y = e->hx; }
+        else if (i + 1 < s.L) { pa.next_w = e->hyb[i + 1].norm1; pa.next_y = e->hx; hx_ready = true; }
+        cb = CombineArgs(); inner_w[0] = inner_w[1] = nullptr;
+        return postnorm_residual(pa, st);
+      }
       if (!hyper) return flush_more();
       StreamCombineArgs sc;
       sc.xs = e->res32; sc.src = cb; sc.y32 = y32_used ? e->y32 : nullptr; sc.col_scale = L.col_scale[sub]; sc.mix = L.hc_mix[sub]; sc.out_w = L.hc_out[sub];
@@ -611,6 +713,74 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
               : attn_bias_chunk(aa, st));
       DENSE(e->obuf1, d, e->mixbuf, ko, L.o, T, ACT_NONE);
       add_src(e->obuf1, d, 1.f);
+    } else if (h.mixer == HybridLayerSpec::WINDOW_GLA || h.mixer == HybridLayerSpec::POOLED) {
+      const bool gla = h.mixer == HybridLayerSpec::WINDOW_GLA;
+      const int nq = h.heads * h.dim, nk = h.kv_heads * h.dim, nv = h.kv_heads * h.vdim, ka = h.heads * h.vdim, ldp = L.proj.N;
+      DENSE(e->pbuf, ldp, e->hx, d, L.proj, T, ACT_NONE);        // every projection of the normed row in one product (biases in)
+      const void* qkv = e->pbuf; int ldq = ldp;
+      if (gla) {
+        ShortConvArgs sc;                                        // q, k and v channels through their short convolutions
+        sc.x = e->pbuf; sc.ldx = ldp; sc.y = e->ubuf; sc.ldy = nq + nk + nv; sc.w = L.conv_w; sc.C = nq + nk + nv; sc.taps = h.conv;
+        sc.state = e->state + L.state_off; sc.slot_stride = e->slot_stride; sc.slots = m.sslot; sc.qsl = m.qsl; sc.positions = m.pos; sc.token_req = m.treq;
+        sc.B = B; sc.T = T; sc.elt = elt;
+        HFWD(C_RGLRU, (double)T * sc.C * 2 * es, 2.0 * T * sc.C * h.conv, short_conv_state(sc, st));
+        ++e->launches;
+        qkv = e->ubuf; ldq = sc.ldy;
+      }
+      HeadRotaryArgs ro;      // per-head q / k norm, rotation in halves, K cache <- keys, V cache <- values (turned by their position)
+      ro.q = const_cast<void*>(qkv); ro.ldq = ldq; ro.k = at(const_cast<void*>(qkv), nq); ro.ldk = ldq; ro.v = at(const_cast<void*>(qkv), nq + nk); ro.ldv = ldq;
+      ro.norm_q = ro.norm_k = h.head_norm; ro.q_norm_w = L.q_norm; ro.k_norm_w = L.k_norm; ro.eps = s.eps;
+      ro.freq = L.rot_freq; ro.rot_dims = h.rot_dims; ro.v_freq = h.v_rot ? L.v_freq : nullptr; ro.positions = m.pos; ro.slots = m.slots;
+      ro.k_cache = L.kc; ro.v_cache = L.vc; ro.T = T; ro.H = h.heads; ro.G = h.kv_heads; ro.dim = h.dim; ro.vdim = h.vdim; ro.block_size = bs; ro.elt = elt;
+      HFWD(C_KVW, (double)T * (2.0 * nq + 2.0 * nk + 2.0 * nv) * es, 0, head_norm_rotary_kvwrite(ro, st));
+      const int ps = h.pool > 0 ? pool_slots_per_block(bs, h.pool) : 0;
+      if (h.pool > 0) {
+        PoolKvArgs pk;       // blocks of `pool` positions that this step completes: their mean key and value
+        pk.k_cache = L.kc; pk.v_cache = L.vc; pk.pk_cache = L.pkc; pk.pv_cache = L.pvc; pk.block_table = m.btab; pk.max_blocks = max_blocks;
+        pk.positions = m.pos; pk.token_req = m.treq; pk.T = T; pk.G = h.kv_heads; pk.dim = h.dim; pk.vdim = h.vdim; pk.block_size = bs; pk.pool = h.pool; pk.pool_slots = ps; pk.elt = elt;
+        HFWD(C_KVW, (double)T * (nk + nv) * es * (1.0 + 1.0 / h.pool), 0, pool_kv_write(pk, st));
+      }
+      AttnBiasArgs aa;
+      aa.q = qkv; aa.ldq = ldq; aa.out = e->mixbuf; aa.ldo = ka; aa.k_cache = L.kc; aa.v_cache = L.vc;
+      aa.block_table = m.btab; aa.max_blocks = max_blocks; aa.seq_lens = m.seq_lens; aa.qsl = m.qsl; aa.positions = m.pos; aa.token_req = m.treq;
+      aa.B = B; aa.T = T; aa.H = h.heads; aa.G = h.kv_heads; aa.dim = h.dim; aa.vdim = h.vdim; aa.block_size = bs; aa.chunk = 0;
+      aa.window = h.window; aa.keep_first = h.keep_first; aa.pool = h.pool; aa.pk_cache = L.pkc; aa.pv_cache = L.pvc; aa.pool_slots = ps;
+      aa.scale = h.scale; aa.bias_span = 0.f; aa.elt = elt;
+      for (int r = 0; r < B; ++r) aa.max_q = std::max(aa.max_q, hm.qsl[r + 1] - hm.qsl[r]);
+      while (aa.num_decode < B && hm.qsl[aa.num_decode + 1] - hm.qsl[aa.num_decode] == 1) ++aa.num_decode;
+      double keys = 0;                                   // visible keys over all rows: the window's tokens and what lies before it
+      for (int t = 0; t < T; ++t) {
+        const int before = std::max(hm.pos[t] - h.window + 1, 0);
+        keys += std::min(hm.pos[t] + 1, h.window) + (h.pool > 0 ? before / h.pool : std::min(before, h.keep_first));
+      }
+      HFWD(decode_only ? C_ATT_DEC : C_ATT_GEN, (decode_only ? keys : (double)T) * h.kv_heads * (h.dim + h.vdim) * es + (double)T * h.heads * (h.dim + h.vdim) * es,
+           2.0 * keys * h.heads * (h.dim + h.vdim), attn_bias_chunk(aa, st));
+      if (h.v_rot) HFWD(C_ACT, (double)T * ka * 2 * es, 0, rotate_heads_halves(e->mixbuf, ka, m.pos, L.v_freq, T, h.heads, h.vdim, -1.f, elt, st));
+      DENSE(e->obuf1, d, e->mixbuf, ka, L.o, T, ACT_NONE);
+      if (gla) {
+        const int mk = h.m_heads * h.m_dim, mv = h.m_heads * h.m_vdim, lr = L.wkv_w2.K;
+        LinearArgs a2;     // the decay's logit: second half of the low-rank pair with its bias, kept in fp32
+        a2.x = at(e->pbuf, L.off_a1); a2.ldx = ldp; a2.w = L.wkv_w2.w; a2.bias = L.wkv_w2.b; a2.y = e->gates32; a2.ldy = mk; a2.T = T; a2.N = mk; a2.K = lr;
+        a2.elt = elt; a2.out_f32 = true;
+        HFWD(C_MLSTM, es * ((double)lr * mk + (double)T * lr) + 4.0 * T * mk, 2.0 * T * (double)mk * lr, linear_any(a2, st));
+        WkvArgs wa;        // gated linear attention: the state is read after the update, the decay is sigmoid(z)^(1 / tau)
+        wa.d = 0; wa.r = at(e->pbuf, L.off_mq); wa.k = at(e->pbuf, L.off_mk); wa.v = at(e->pbuf, L.off_mv); wa.gate_pre = at(e->pbuf, L.off_mg); wa.ld = ldp;
+        wa.decay_pre = e->gates32; wa.u = nullptr; wa.norm_w = L.wkv_norm; wa.o32 = e->mo32; wa.out = e->mixbuf2; wa.ldo = mv;
+        wa.state = e->state + L.state_off + short_conv_state_floats(nq + nk + nv, h.conv); wa.slot_stride = e->slot_stride;
+        wa.slots = m.sslot; wa.qsl = m.qsl; wa.positions = m.pos; wa.token_req = m.treq;
+        wa.B = B; wa.T = T; wa.H = h.m_heads; wa.dim = h.m_dim; wa.vdim = h.m_vdim; wa.eps = s.eps; wa.elt = elt;
+        wa.decay_mode = 1; wa.tau = h.tau; wa.read_after = true; wa.r_scale = 1.f / sqrtf((float)h.m_dim);
+        for (int r = 0; r < B; ++r) wa.max_q = std::max(wa.max_q, hm.qsl[r + 1] - hm.qsl[r]);
+        HFWD(C_MLSTM, 2.0 * B * gla_state_floats(h.m_heads, h.m_dim, h.m_vdim) * 4 + (double)T * ((2.0 * mk + 3.0 * mv) * es + 4.0 * mk + 8.0 * mv),
+             4.0 * T * h.m_heads * (double)h.m_dim * h.m_vdim, wkv_scan(wa, st));
+        ++e->launches;
+        DENSE(e->obuf2, d, e->mixbuf2, mv, L.o2, T, ACT_NONE);
+        // half the sum of the two sides, each RMS-normed over the width with its own weight
+        add_src(e->obuf1, d, 0.5f); add_src(e->obuf2, d, 0.5f);
+        inner_w[0] = L.side_norm[0]; inner_w[1] = L.side_norm[1];
+      } else {
+        add_src(e->obuf1, d, 1.f);
+      }
     } else if (h.mixer == HybridLayerSpec::WKV) {
       const int hd = h.heads * h.dim, lr = L.wkv_w1.N;
       WkvArgs wa;
@@ -715,9 +885,17 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       // the feed-forward reads a norm of the stream that already holds the mixer's output
       { const double nsrc = cb.n; HFWD(C_ACT, Td * (8.0 * S + nsrc * es), 0, flush()); }
       sub = 1;
-      if (!hyper) HFWD(C_NORM, Td * (4 + es), 0, layer_norm(e->hx, nullptr, L.norm2, T, 1.f));
+      if (!hyper && !s.hyb_postnorm) HFWD(C_NORM, Td * (4 + es), 0, layer_norm(e->hx, nullptr, L.norm2, T, 1.f));
     }
-    if (h.mlp == HybridLayerSpec::DENSE && h.ff_limit > 0.f) {
+    if (h.mlp == HybridLayerSpec::DENSE && h.ff_silu_bias) {
+      // silu(gate h + b) * (up h + b): one product over [gate | up] with the biases, the pair formed from its rows
+      const int f = h.ff;
+      void* act = at(e->ffbuf, (int64_t)2 * f * T);
+      DENSE(e->ffbuf, 2 * f, e->hx, d, L.up, T, ACT_NONE);
+      HFWD(C_ACT, (double)T * f * 3 * es, 0, silu_mul_halves(act, e->ffbuf, T, f, elt, st));
+      DENSE(e->obuf2, d, act, f, L.down, T, ACT_NONE);
+      add_src(e->obuf2, d, 1.f);
+    } else if (h.mlp == HybridLayerSpec::DENSE && h.ff_limit > 0.f) {
       // clamped gated unit: bfloat16 forms the pair in the epilogue of the tensor-core GEMM over [gate | up]
       const int f = h.ff;
       const double gb = es * (2.0 * f * d + (double)T * (d + f)), gf = 4.0 * T * (double)f * d;

@@ -1,8 +1,10 @@
 // Launchers of the kernels that layer-list ("hybrid") models add to the library: a shape-agnostic linear layer with
 // grouped / gathered rows, fp32-residual norms, biased chunk-masked paged attention (soft cap, sink logits), rotary
 // positions with a whole-projection norm, the gated linear recurrence (RG-LRU), the matrix memory (mLSTM), the
-// mixture-of-experts router, the hyper-connected residual (several streams), the WKV recurrence and the row-wise parts of
-// attention through latents.  Every mechanism takes its sizes and constants
+// mixture-of-experts router, the hyper-connected residual (several streams), the WKV recurrence (also run as gated linear
+// attention), the row-wise parts of attention through latents, sliding windows with kept first tokens or pooled blocks,
+// short causal convolutions with a state, per-head norms with rotary positions in halves and rotated values, and grouped
+// RMS norms before and after a sublayer.  Every mechanism takes its sizes and constants
 // as arguments.  `elt` names the storage type of activations and weights: KGE_ELT_BF16 or KGE_ELT_F32; what the
 // mechanisms compute in 32 bits (softmax, norms, routers, residual sums, recurrent state and everything that enters a
 // recurrence besides projections and short convolutions) is 32-bit in both.
@@ -57,6 +59,37 @@ struct CombineArgs {
   int n = 0;
 };
 int residual_combine(float* res, const CombineArgs& a, int T, int d, int elt, cudaStream_t st);
+// RMS norm in groups: the row is cut into `groups` equal consecutive parts, each divided by its own
+// sqrt(mean(part^2) + eps); the whole is multiplied by w (as it is) and out_scale.  x fp32, y in elt.
+int group_rmsnorm_f32in(void* y, const float* x, const int32_t* rows, const void* w, int R, int d, int groups, float eps, float out_scale, int elt,
+                        cudaStream_t st);
+// A sublayer's result joins the residual stream through a norm of its own, and the next sublayer's input is formed in the same pass:
+//   y[t, :]   = src_scale * sum_i (inner_w[i] ? src_i[t, :] / sqrt(mean(src_i[t, :]^2) + eps) * inner_w[i] : src_i[t, :])      (nsrc <= 2)
+//   res[t, :] += gn(y[t, :]) * post_w           gn: the group norm above
+//   next_y[t, :] = gn(res[t, :]) * next_w       (next_w != null; next_y in elt)
+// Sources and weights in elt, statistics and sums in fp32.
+struct PostNormArgs {
+  float* res = nullptr;
+  const void* src[2] = {nullptr, nullptr}; int ld[2] = {0, 0}; const void* inner_w[2] = {nullptr, nullptr}; int nsrc = 1; float src_scale = 1.f;
+  const void* post_w = nullptr; const void* next_w = nullptr; void* next_y = nullptr;
+  int T = 0, d = 0, groups = 1; float eps = 1e-5f; int elt = KGE_ELT_BF16;
+};
+int postnorm_residual(const PostNormArgs& a, cudaStream_t st);
+// Causal convolution over time on `C` neighbouring columns of x (row stride ldx), written to y (row stride ldy):
+//   y_t[c] = sum_j w[c, j] * x_(t - taps + 1 + j)[c],   w [C, taps], zeros before position 0;
+// inputs before a request's first row of this step come from its state slot, which holds the last taps - 1 input rows
+// (fp32 [taps - 1, C], oldest first) and is brought up to date at the end.  Sums in fp32, ascending j.
+struct ShortConvArgs {
+  const void* x = nullptr; int ldx = 0; void* y = nullptr; int ldy = 0; const void* w = nullptr; int C = 0, taps = 1;
+  float* state = nullptr; int64_t slot_stride = 0;
+  const int32_t* slots = nullptr; const int32_t* qsl = nullptr; const int32_t* positions = nullptr; const int32_t* token_req = nullptr;
+  int B = 0, T = 0; int elt = KGE_ELT_BF16;
+};
+int short_conv_state(const ShortConvArgs& a, cudaStream_t st);
+inline int64_t short_conv_state_floats(int C, int taps) { return (int64_t)C * (taps - 1); }
+// y[t, n] = silu(gu[t, n]) * gu[t, f + n], n < f (gu [T, 2 f] in elt, the activation in fp32, one rounding)
+int silu_mul_halves(void* y, const void* gu, int T, int f, int elt, cudaStream_t st);
+
 // fp32 [R, V] -> 16-bit logits for the samplers (ld_out >= V)
 int logits_to_elt16(void* out, const float* in, int R, int V, int ld_out, bool f16, cudaStream_t st);
 int elt16_to_f32(float* out, const void* in_bf16, int64_t n, cudaStream_t st);
@@ -69,7 +102,12 @@ int softcap_rows(float* l32, void* l16, int R, int V, int ld16, float cap, cudaS
 //   cap(s) = softcap * tanh(s / softcap) (softcap = 0: s).  With `sinks` (fp32 [H]) the softmax denominator of head h
 //   also holds exp(sinks[h]): a logit without key or value, neither scaled nor capped.
 //   j visible to i iff j <= i and (chunk == 0 or floor(i / chunk) == floor(j / chunk)), positions counted from the
-//   start of the sequence.  Softmax in fp32.  q rows are read from a packed projection buffer (row stride ldq elements,
+//   start of the sequence.  With window > 0 only j > i - window is visible that way, and beside those keys either
+//   (keep_first > 0) the positions j < keep_first that have left the window, with their own keys and values, or
+//   (pool > 0) entry b of the pooled caches for every b < floor((i - window + 1) / pool): one key / value per block of
+//   `pool` positions that lies wholly before the window (pool_kv_write makes them).  All of a row's keys share one
+//   softmax; the distance bias is not defined for kept or pooled keys (bias_span must be 0 with a window).
+//   Softmax in fp32.  q rows are read from a packed projection buffer (row stride ldq elements,
 //   head h at column h * dim); K cache [num_blocks, G, block_size, dim], V cache [num_blocks, G, block_size, vdim].
 //   out [T, H * vdim] (row stride ldo), multiplied by out_scale.
 struct AttnBiasArgs {
@@ -84,9 +122,24 @@ struct AttnBiasArgs {
                                            // while requests with many rows give each warp 16 rows of a shared key tile
   float scale = 1.f, bias_span = 0.f, out_scale = 1.f, softcap = 0.f;
   const float* sinks = nullptr;
+  int window = 0, keep_first = 0, pool = 0;
+  const void* pk_cache = nullptr; const void* pv_cache = nullptr;     // pooled caches [num_blocks, G, pool_slots, dim / vdim]
+  int pool_slots = 0;                      // pooled entries per page: entry b of a request lives in its page b / pool_slots
   int elt = KGE_ELT_BF16;
 };
 int attn_bias_chunk(const AttnBiasArgs& a, cudaStream_t st);
+inline int pool_slots_per_block(int block_size, int pool) { return (block_size + pool - 1) / pool; }
+// Pooled keys and values: for every token of the step whose position p ends a block of `pool` positions
+// ((p + 1) % pool == 0), entry b = p / pool of the pooled caches <- the mean (fp32, positions in ascending order, one
+// rounding to the storage type) of the `pool` cached keys / values of positions b * pool .. p, read through the block
+// table.  Runs after the step's keys and values are in the caches.
+struct PoolKvArgs {
+  const void* k_cache = nullptr; const void* v_cache = nullptr; void* pk_cache = nullptr; void* pv_cache = nullptr;
+  const int32_t* block_table = nullptr; int max_blocks = 0; const int32_t* positions = nullptr; const int32_t* token_req = nullptr;
+  int T = 0, G = 0, dim = 0, vdim = 0, block_size = 0, pool = 1, pool_slots = 1;
+  int elt = KGE_ELT_BF16;
+};
+int pool_kv_write(const PoolKvArgs& a, cudaStream_t st);
 // k / v rows of a packed projection buffer -> paged caches (slot = block * block_size + offset, < 0 skips)
 int kv_write_any(const void* k, int ldk, const void* v, int ldv, const int64_t* slots, void* k_cache, void* v_cache, int T, int G,
                  int dim, int vdim, int block_size, int elt, cudaStream_t st);
@@ -110,6 +163,24 @@ struct RotaryArgs {
   int elt = KGE_ELT_BF16;
 };
 int rotary_norm_kvwrite(const RotaryArgs& a, cudaStream_t st);
+// The same pass with norms per head and pairs in halves.  q [T, H * dim] and k [T, G * dim] are RMS-normed per head
+// (norm_q / norm_k; the weight of `dim` numbers is shared by all heads, null = no weight), then the first rot_dims
+// dimensions of every head turn in pairs (i, i + rot_dims / 2) by position * freq[i]; q is written back in place, k goes
+// to the key cache.  v [T, G * vdim] goes to the value cache as it is, or (v_freq != null) with ALL vdim dimensions turned
+// in pairs (m, m + vdim / 2) by position * v_freq[m].  Norm statistics, angles (double precision) and rotation in fp32.
+struct HeadRotaryArgs {
+  void* q = nullptr; int ldq = 0; const void* k = nullptr; int ldk = 0; const void* v = nullptr; int ldv = 0;
+  bool norm_q = false, norm_k = false; const void* q_norm_w = nullptr; const void* k_norm_w = nullptr; float eps = 1e-5f;
+  const double* freq = nullptr; int rot_dims = 0; const double* v_freq = nullptr;
+  const int32_t* positions = nullptr; const int64_t* slots = nullptr;
+  void* k_cache = nullptr; void* v_cache = nullptr;
+  int T = 0, H = 0, G = 0, dim = 0, vdim = 0, block_size = 0;
+  int elt = KGE_ELT_BF16;
+};
+int head_norm_rotary_kvwrite(const HeadRotaryArgs& a, cudaStream_t st);
+// x[t, h, :n] (row stride ldx, head h at column h * n) turns in pairs (m, m + n / 2) by sign * position[t] * freq[m], in place
+int rotate_heads_halves(void* x, int ldx, const int32_t* positions, const double* freq, int T, int H, int n, float sign, int elt, cudaStream_t st);
+
 // freq[i] = base^(-2i / dims), i < dims / 2; with YaRN scaling (factor > 0): ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)
 // between lo = max(floor(c(fast)), 0) and hi = min(ceil(c(slow)), dims - 1), c(t) = dims * ln(original / (2 pi t)) / (2 ln base);
 // freq_i <- freq_i / factor * ramp_i + freq_i * (1 - ramp_i) and *mult = 0.1 ln(factor) + 1 (else 1).  Host only.
@@ -221,11 +292,16 @@ struct WkvArgs {
   int B = 0, T = 0, H = 0, dim = 0;
   int max_q = 0;                           // the longest request's rows in this step (0 = unknown: token by token)
   float eps = 1e-5f;
+  // gated linear attention on the same kernels: value size vdim (0 = dim; S is [dim, vdim], v / gate_pre / out / o32 /
+  // norm_w rows are H * vdim wide), decay_mode 1: w_t = sigmoid(decay_pre_t)^(1 / tau) = exp(logsigmoid(decay_pre_t) / tau),
+  // read_after: o_t = S_t^T r_t with S_t the state AFTER the update (no bonus u), r multiplied by r_scale in fp32
+  int vdim = 0, decay_mode = 0; bool read_after = false; float tau = 1.f, r_scale = 1.f;
   int elt = KGE_ELT_BF16;
 };
 int wkv_shift_mix(const WkvArgs& a, cudaStream_t st);
 int wkv_scan(const WkvArgs& a, cudaStream_t st);
 inline int64_t wkv_state_floats(int d, int H, int dim) { return (int64_t)d + (int64_t)H * dim * dim; }
+inline int64_t gla_state_floats(int H, int dim, int vdim) { return (int64_t)H * dim * vdim; }     // WkvArgs with d = 0
 
 // Attention through latents, the parts around the attention kernel.
 //   segment_rmsnorm: up to two column ranges of the rows of x (elt, row stride ldx) are RMS-normed in fp32 and written

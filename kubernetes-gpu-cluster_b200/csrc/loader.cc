@@ -243,8 +243,71 @@ static bool parse_zezilix(const Json& j, ModelSpec* s, std::string* err) {
   return true;
 }
 
+// Balenex: a layer list of 'parallel' mixers (windowed attention with kept first tokens, short convolutions, per-head
+// q / k norm, rotary positions in halves and rotated values, beside gated linear attention) and 'attention' mixers
+// (windowed attention that also sees one pooled key / value per block of older positions), gated silu feed-forwards with
+// biases, and grouped RMS norms before and after every sublayer.
+static bool parse_attention_sizes(const Json& m, HybridLayerSpec* h) {
+  h->heads = (int)m.int_or("heads", 0); h->kv_heads = (int)m.int_or("kv_heads", h->heads);
+  h->dim = (int)m.int_or("dim", 0); h->vdim = (int)m.int_or("vdim", h->dim);
+  h->scale = (float)m.num_or("scale", 1.0);
+  if (const Json* mk = m.get("mask")) if (mk->is_obj()) {
+    h->window = (int)mk->int_or("size", 0); h->keep_first = (int)mk->int_or("keep_first", 0); h->pool = (int)mk->int_or("pool", 0);
+  }
+  return h->heads > 0 && h->kv_heads > 0 && h->heads % h->kv_heads == 0 && h->dim > 0 && h->vdim > 0 && h->window > 0 && h->keep_first >= 0 && h->pool >= 0;
+}
+
+static bool parse_balenex(const Json& j, ModelSpec* s, std::string* err) {
+  s->model_type = "balenex";
+  s->vocab = (int)j.int_or("vocab", 0);
+  s->d = (int)j.int_or("width", 0);
+  if (const Json* n = j.get("norm")) { s->eps = (float)n->num_or("eps", 1e-5); s->norm_groups = (int)n->int_or("groups", 1); }
+  s->hyb_prenorm_pair = s->hyb_postnorm = true;
+  s->max_pos = 1 << 20;                 // rotary angles are computed from the position: no table bounds them
+  s->torch_dtype = "bfloat16";
+  s->bos = (int)j.int_or("bos_token_id", -1);
+  s->eos = (int)j.int_or("eos_token_id", -1);
+  if (s->vocab <= 0 || s->d <= 0) { *err = "config.json misses a required size"; return false; }
+  if (s->norm_groups < 1 || s->d % s->norm_groups) { *err = "config.json: 'norm.groups' must divide the width"; return false; }
+  const Json* ls = j.get("layers");
+  if (!ls || !ls->is_arr() || ls->arr.empty()) { *err = "config.json: 'layers' must be a non-empty array"; return false; }
+  for (const Json& l : ls->arr) {
+    HybridLayerSpec h;
+    const std::string type = l.str_or("type", "");
+    const Json* m = l.get("mixer");
+    if (!m || !m->is_obj()) { *err = "config.json: a layer has no 'mixer'"; return false; }
+    if (type == "parallel") {
+      h.mixer = HybridLayerSpec::WINDOW_GLA;
+      const Json *a = m->get("left"), *r = m->get("right");
+      if (!a || !a->is_obj() || !r || !r->is_obj()) { *err = "config.json: a parallel mixer needs 'left' and 'right'"; return false; }
+      if (!parse_attention_sizes(*a, &h) || h.pool != 0) { *err = "config.json: bad sizes of the attention side"; return false; }
+      h.conv = (int)a->int_or("conv", 1);
+      h.head_norm = h.rot_halves = h.v_rot = true;
+      if (const Json* ro = a->get("rot")) if (ro->is_obj()) { h.rot_dims = (int)ro->int_or("dims", 0); h.rot_base = ro->num_or("base", 10000.0); }
+      if (h.conv < 1 || h.conv > 16 || h.rot_dims < 0 || h.rot_dims > h.dim || h.rot_dims % 2 || h.vdim % 2 || h.rot_base <= 0.0) {
+        *err = "config.json: bad conv / rotary sizes of the attention side (vdim and rot.dims are even, 1 <= conv <= 16)"; return false;
+      }
+      h.m_heads = (int)r->int_or("heads", 0); h.m_dim = (int)r->int_or("dim", 0); h.m_vdim = (int)r->int_or("vdim", h.m_dim);
+      h.tau = (float)r->num_or("tau", 1.0);
+      h.decay_rank = (int)r->int_or("decay_rank", 0);
+      if (h.m_heads <= 0 || h.m_dim <= 0 || h.m_vdim <= 0 || !(h.tau > 0.f)) { *err = "config.json: bad sizes of the linear-attention side"; return false; }
+    } else if (type == "attention") {
+      h.mixer = HybridLayerSpec::POOLED;
+      if (!parse_attention_sizes(*m, &h) || h.pool < 1 || h.keep_first != 0) { *err = "config.json: bad attention sizes (mask.size and mask.pool are positive)"; return false; }
+      h.head_norm = true;
+    } else { *err = "config.json: unknown layer type '" + type + "' (parallel, attention)"; return false; }
+    if (!parse_hybrid_mlp(l, &h, err)) return false;
+    if (h.mlp == HybridLayerSpec::MOE) { *err = "config.json: this architecture has no mixture of experts"; return false; }
+    if (h.mlp == HybridLayerSpec::DENSE) h.ff_silu_bias = true;
+    s->hybrid.push_back(h);
+  }
+  s->L = (int)s->hybrid.size();
+  return true;
+}
+
 static bool parse_config(const Json& j, ModelSpec* s, std::string* err) {
   if (j.str_or("architecture", "") == "Safupel") return parse_hybrid(j, s, err);
+  if (j.str_or("architecture", "") == "Balenex") return parse_balenex(j, s, err);
   if (j.str_or("architecture", "") == "Girolorn") return parse_girolorn(j, s, err);
   if (j.str_or("architecture", "") == "Zezilix") return parse_zezilix(j, s, err);
   s->model_type = j.str_or("model_type", "");
@@ -482,16 +545,20 @@ extern "C" int kge_model_spec_json(const kge_model_dir* m, char* out, int cap) {
                "\"mlp\":%d,\"ff\":%d,\"experts\":%d,\"top\":%d,\"expert_ff\":%d,\"shared_ff\":%d,\"softcap\":%.9g,\"rot_dims\":%d,\"rot_base\":%.17g,"
                "\"yarn_factor\":%.17g,\"yarn_original\":%.17g,\"yarn_fast\":%.17g,\"yarn_slow\":%.17g,\"route\":%d,\"glu\":%d,\"expert_limit\":%.9g,"
                "\"shared_limit\":%.9g,\"weights_of\":%d,\"tensor_index\":%d,\"q_rank\":%d,\"kv_rank\":%d,\"rot_part\":%d,\"out_gate\":%d,"
-               "\"decay_rank\":%d,\"ff_limit\":%.9g,\"router_scale\":%.9g}",
+               "\"decay_rank\":%d,\"ff_limit\":%.9g,\"router_scale\":%.9g,\"window\":%d,\"keep_first\":%d,\"pool\":%d,\"tau\":%.9g,"
+               "\"head_norm\":%d,\"rot_halves\":%d,\"v_rot\":%d,\"ff_silu_bias\":%d}",
                i ? "," : "", h.mixer, h.width, h.blocks, h.conv, h.heads, h.kv_heads, h.dim, h.vdim, h.chunk, (double)h.scale, (double)h.left_scale,
                (double)h.right_scale, h.m_heads, h.m_dim, h.m_vdim, (double)h.gate_cap, h.mlp, h.ff, h.experts, h.top, h.expert_ff, h.shared_ff,
                (double)h.softcap, h.rot_dims, h.rot_base, h.yarn_factor, h.yarn_original, h.yarn_fast, h.yarn_slow, h.route, h.glu, (double)h.expert_limit,
                (double)h.shared_limit, h.weights_of, h.tensor_index < 0 ? (int)i : h.tensor_index, h.q_rank, h.kv_rank, h.rot_part, h.out_gate ? 1 : 0,
-               h.decay_rank, (double)h.ff_limit, (double)h.router_scale);
+               h.decay_rank, (double)h.ff_limit, (double)h.router_scale, h.window, h.keep_first, h.pool, (double)h.tau, h.head_norm ? 1 : 0,
+               h.rot_halves ? 1 : 0, h.v_rot ? 1 : 0, h.ff_silu_bias ? 1 : 0);
       j += buf;
     }
-    snprintf(buf, sizeof buf, "],\"eps\":%.9g,\"logit_scale\":%.9g,\"logit_softcap\":%.9g,\"streams\":%d,\"residual_mult\":%.9g,\"embed_norm\":%s}", (double)s.eps,
-             (double)s.logit_scale, (double)s.logit_softcap, s.streams, (double)s.residual_mult, s.embed_norm ? "true" : "false");
+    snprintf(buf, sizeof buf, "],\"eps\":%.9g,\"logit_scale\":%.9g,\"logit_softcap\":%.9g,\"streams\":%d,\"residual_mult\":%.9g,\"embed_norm\":%s,"
+             "\"norm_groups\":%d,\"postnorm\":%s}", (double)s.eps,
+             (double)s.logit_scale, (double)s.logit_softcap, s.streams, (double)s.residual_mult, s.embed_norm ? "true" : "false", s.norm_groups,
+             s.hyb_postnorm ? "true" : "false");
     j += buf;
     KGE_REQUIRE((int)j.size() < cap, "kge_model_spec_json: buffer of %d bytes too small", cap);
     memcpy(out, j.c_str(), j.size() + 1);

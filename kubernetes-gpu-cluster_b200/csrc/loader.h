@@ -12,7 +12,7 @@ namespace kge {
 // One layer of a layer-list ("hybrid") model: which token mixer it has, that mixer's sizes and constants, and its
 // feed-forward.  Every number comes from config.json; the kernels take them as parameters.
 struct HybridLayerSpec {
-  enum Mixer { RGLRU = 0, PARALLEL = 1, ATTENTION = 2, WKV = 3, LATENT = 4 };
+  enum Mixer { RGLRU = 0, PARALLEL = 1, ATTENTION = 2, WKV = 3, LATENT = 4, WINDOW_GLA = 5, POOLED = 6 };
   enum Mlp { NONE = 0, DENSE = 1, MOE = 2 };
   int mixer = RGLRU;
   // gated linear recurrence (RG-LRU): two branches of `width`, gates block-diagonal in `blocks` parts, causal conv of `conv` taps
@@ -44,10 +44,27 @@ struct HybridLayerSpec {
   // sigmoid(W_g h) before the output matrix.  heads = kv_heads, dim counts the whole key, vdim the value.
   int q_rank = 0, kv_rank = 0, rot_part = 0;
   bool out_gate = false;
+  // windowed attention beside gated linear attention (WINDOW_GLA), both reading the same row; each side's output is
+  // RMS-normed over the model width with a weight of its own and the mixer's result is half their sum.
+  //   attention side (heads / kv_heads / dim / vdim / scale / rot_dims / rot_base as above): q, k and v carry biases and pass a
+  //   causal convolution of `conv` taps per channel; q and k are RMS-normed per head with one weight of `dim` numbers
+  //   (head_norm); rotary positions act on the first rot_dims dimensions of a head in pairs (i, i + rot_dims / 2)
+  //   (rot_halves); the values turn over all vdim dimensions by their own position before they are cached and the head's
+  //   output turns back by the query's position (v_rot); position i sees j <= i with i - j < window or j < keep_first.
+  //   linear-attention side: m_heads x (m_dim x m_vdim) state, q scaled by m_dim^(-1/2), a decay per key channel
+  //   sigmoid(z)^(1 / tau) whose logit z comes through a low-rank pair with a bias, read-out after the update, a per-head
+  //   RMS norm (one weight of m_vdim numbers) and a silu gate.
+  // windowed attention over pooled blocks (POOLED): q, k, v and the output carry biases; q and k are divided by their
+  // root mean square per head (head_norm without a weight); no rotation; position i sees j with 0 <= i - j < window
+  // and one key / value - the mean of the cached ones - for every block of `pool` positions that ends at or before i - window.
+  int window = 0, keep_first = 0, pool = 0;
+  bool head_norm = false, rot_halves = false, v_rot = false;
+  float tau = 1.f;
   // feed-forward
   int mlp = NONE;
   int ff = 0;                                    // dense
   float ff_limit = 0.f;                          // dense: > 0 - a clamped gated unit (gate, up, down) with this limit; 0 - up, GELU, down
+  bool ff_silu_bias = false;                     // dense: down(silu(gate h + b) * (up h + b)) + b, every projection with a bias
   int experts = 0, top = 0, expert_ff = 0, shared_ff = 0;   // mixture of experts (+ an always-on shared expert if shared_ff > 0)
   // how the experts are chosen and weighed: ROUTE_SIGMOID_IN - sigmoid scores, the weight multiplies the expert's input;
   // ROUTE_SOFTMAX_TOP - the largest logits (router bias added), softmax over the chosen logits only, the weight multiplies
@@ -67,11 +84,11 @@ struct HybridLayerSpec {
   bool shared_gate = false;                      // the shared expert's output is multiplied by sigmoid(w_sg . h), one number per token
   int weights_of = -1;                           // >= 0: this layer owns no tensors and runs with that layer's (cache and state stay its own)
   int tensor_index = -1;                         // the 'l<i>.' prefix of this layer's tensors (-1: its place in the list)
-  bool has_cache() const { return mixer == PARALLEL || mixer == ATTENTION || mixer == LATENT; }
+  bool has_cache() const { return mixer == PARALLEL || mixer == ATTENTION || mixer == LATENT || mixer == WINDOW_GLA || mixer == POOLED; }
 };
 
 struct ModelSpec {
-  std::string model_type;       // "opt" | "llama" | "qwen2" | "qwen3" | "safupel" | "girolorn" | "zezilix"
+  std::string model_type;       // "opt" | "llama" | "qwen2" | "qwen3" | "safupel" | "girolorn" | "zezilix" | "balenex"
   // layer-list models (config.json "architecture"): per-layer descriptions and the multiplier of the logits
   std::vector<HybridLayerSpec> hybrid;
   float logit_scale = 1.f;
@@ -80,6 +97,11 @@ struct ModelSpec {
   // (hyb_prenorm_pair) a norm before the mixer and, after the mixer's sum, another before the feed-forward;
   // hyb_layernorm: mean-centred layer norm with a weight and no bias instead of the RMS norm
   bool hyb_prenorm_pair = false, hyb_layernorm = false;
+  // norm_groups > 1: an RMS norm cuts its row into that many equal consecutive parts and divides each by its own root
+  // mean square; hyb_postnorm: every sublayer's result goes through a norm of its own (weights norm1b / norm2b) before it
+  // is added to the residual stream; norm weights multiply as they are
+  int norm_groups = 1;
+  bool hyb_postnorm = false;
   // hyper-connected residual: `streams` >= 1 copies of the residual stream, read through per-sublayer input weights,
   // mixed by a streams x streams matrix and written through output weights (0: one plain residual stream); every
   // sublayer's result is multiplied by residual_mult and, element by element, by a per-layer scale vector; the

@@ -214,4 +214,111 @@ int rotary_norm_kvwrite(const RotaryArgs& a, cudaStream_t st) {
   return 0;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Norms per head and rotation in halves.  One block per token, one warp per head in turn (q heads, then key heads, then
+// value heads): the warp sums the head's squares (fp32), then walks the head's pairs (i, i + rot_dims / 2); dimensions
+// beyond rot_dims pass with the norm only.  Values turn over their whole width by the token's own position.  The token's
+// cos / sin tables (rot_dims / 2 entries for q and k, vdim / 2 for the values) are formed once per block.
+template <typename E>
+__global__ void __launch_bounds__(256) head_norm_rotary_kvwrite_kernel(HeadRotaryArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float hcs[];                // [half] cos, [half] sin, [vhalf] cos, [vhalf] sin
+  const int t = blockIdx.x, half = a.rot_dims >> 1, vhalf = a.v_freq ? a.vdim >> 1 : 0;
+  float *qc = hcs, *qs = hcs + half, *vcs = hcs + 2 * half, *vsn = vcs + vhalf;
+  const int pos = a.positions[t];
+  for (int i = threadIdx.x; i < half + vhalf; i += blockDim.x) {
+    float s, c;
+    if (i < half) { sincos_reduced((double)pos * a.freq[i], &s, &c); qc[i] = c; qs[i] = s; }
+    else { sincos_reduced((double)pos * a.v_freq[i - half], &s, &c); vcs[i - half] = c; vsn[i - half] = s; }
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int64_t slot = a.slots ? a.slots[t] : -1;
+  const int64_t blk = slot >= 0 ? slot / a.block_size : 0, off = slot >= 0 ? slot % a.block_size : 0;
+  const int heads = a.H + a.G + (a.v ? a.G : 0);
+  for (int hh = warp; hh < heads; hh += nw) {
+    if (hh < a.H + a.G) {
+      const bool isq = hh < a.H;
+      const int h = isq ? hh : hh - a.H;
+      const E* src = isq ? (const E*)a.q + (int64_t)t * a.ldq + h * a.dim : (const E*)a.k + (int64_t)t * a.ldk + h * a.dim;
+      const bool norm = isq ? a.norm_q : a.norm_k;
+      const E* w = (const E*)(isq ? a.q_norm_w : a.k_norm_w);
+      float inv = 1.f;
+      if (norm) {
+        float ss = 0.f;
+        for (int c = lane; c < a.dim; c += 32) { const float v = ldf(src + c); ss = fmaf(v, v, ss); }
+        inv = 1.f / sqrtf(warp_sum(ss) / (float)a.dim + a.eps);
+      }
+      E* dst = nullptr;
+      if (isq) dst = (E*)a.q + (int64_t)t * a.ldq + h * a.dim;
+      else if (slot >= 0) dst = (E*)a.k_cache + ((blk * a.G + h) * a.block_size + off) * a.dim;
+      if (!dst) continue;
+      // every lane reads both numbers of its pairs before it writes them (q is rewritten in place)
+      for (int i = lane; i < half; i += 32) {
+        const float u = ldf(src + i) * inv * (w ? ldf(w + i) : 1.f), v = ldf(src + half + i) * inv * (w ? ldf(w + half + i) : 1.f);
+        stf(dst + i, u * qc[i] - v * qs[i]);
+        stf(dst + half + i, v * qc[i] + u * qs[i]);
+      }
+      for (int c = 2 * half + lane; c < a.dim; c += 32) stf(dst + c, ldf(src + c) * inv * (w ? ldf(w + c) : 1.f));
+    } else if (slot >= 0) {
+      const int g = hh - a.H - a.G;
+      const E* src = (const E*)a.v + (int64_t)t * a.ldv + g * a.vdim;
+      E* dst = (E*)a.v_cache + ((blk * a.G + g) * a.block_size + off) * a.vdim;
+      if (a.v_freq) {
+        for (int i = lane; i < vhalf; i += 32) {
+          const float u = ldf(src + i), v = ldf(src + vhalf + i);
+          stf(dst + i, u * vcs[i] - v * vsn[i]);
+          stf(dst + vhalf + i, v * vcs[i] + u * vsn[i]);
+        }
+      } else {
+        for (int c = lane; c < a.vdim; c += 32) dst[c] = src[c];
+      }
+    }
+  }
+}
+
+int head_norm_rotary_kvwrite(const HeadRotaryArgs& a, cudaStream_t st) {
+  if (a.T <= 0) return 0;
+  KGE_REQUIRE(a.rot_dims >= 0 && a.rot_dims % 2 == 0 && a.rot_dims <= a.dim && (a.rot_dims == 0 || a.freq) && (!a.v_freq || a.vdim % 2 == 0),
+              "head_norm_rotary_kvwrite: %d of %d dimensions turn (values: %d)", a.rot_dims, a.dim, a.vdim);
+  const size_t smem = (size_t)(a.rot_dims + (a.v_freq ? a.vdim : 0)) * 4;
+  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(head_norm_rotary_kvwrite_kernel<float>, dim3(a.T), dim3(256), smem, st, a)
+                                        : launch_pdl(head_norm_rotary_kvwrite_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), smem, st, a);
+  KGE_CUDA_OK(ce);
+  return 0;
+}
+
+// one block per token, one warp per head in turn
+template <typename E>
+__global__ void __launch_bounds__(256) rotate_heads_halves_kernel(E* x, int ldx, const int32_t* positions, const double* freq, int H, int n, float sign) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float rcs[];                // [n / 2] cos, then sin
+  const int t = blockIdx.x, half = n >> 1;
+  const int pos = positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float s, c;
+    sincos_reduced((double)pos * freq[i], &s, &c);
+    rcs[i] = c; rcs[half + i] = sign * s;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx % half;
+    E* p = x + (int64_t)t * ldx + h * n;
+    const float u = ldf(p + i), v = ldf(p + half + i);
+    stf(p + i, u * rcs[i] - v * rcs[half + i]);
+    stf(p + half + i, v * rcs[i] + u * rcs[half + i]);
+  }
+}
+
+int rotate_heads_halves(void* x, int ldx, const int32_t* positions, const double* freq, int T, int H, int n, float sign, int elt, cudaStream_t st) {
+  if (T <= 0 || n < 2) return 0;
+  KGE_REQUIRE(n % 2 == 0 && freq, "rotate_heads_halves: %d dimensions", n);
+  cudaError_t ce = elt == KGE_ELT_F32 ? launch_pdl(rotate_heads_halves_kernel<float>, dim3(T), dim3(256), (size_t)n * 4, st, (float*)x, ldx, positions, freq, H, n, sign)
+                                      : launch_pdl(rotate_heads_halves_kernel<__nv_bfloat16>, dim3(T), dim3(256), (size_t)n * 4, st, (__nv_bfloat16*)x, ldx, positions, freq, H, n, sign);
+  KGE_CUDA_OK(ce);
+  return 0;
+}
+
 }  // namespace kge

@@ -11,6 +11,13 @@
 
 namespace kge {
 
+// the decay of a key channel from its logit: exp(-exp(z)), or (mode 1) sigmoid(z)^(1 / tau); log_decay is its natural logarithm
+__device__ __forceinline__ float log_decay(float z, int mode, float tau) {
+  if (mode == 0) return -expf(z);
+  const float ls = z < 0.f ? z - log1pf(expf(z)) : -log1pf(expf(-z));      // log(sigmoid(z)) without overflow on either side
+  return ls / tau;
+}
+
 // One block per token.  The row before a request's first row of this step comes from the slot (zeros at position 0);
 // nothing is written to the slot here, so the blocks of a request do not race with it.
 template <typename E>
@@ -96,29 +103,31 @@ __global__ void __launch_bounds__(MAXD) wkv_scan_kernel(WkvArgs a) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ __align__(16) float rs[2][MAXD], ks[2][MAXD], ws[2][MAXD], us[MAXD];
-  const int b = blockIdx.x, h = blockIdx.y, j = threadIdx.x, dim = a.dim, HD = a.H * a.dim;
+  const int b = blockIdx.x, h = blockIdx.y, j = threadIdx.x, dim = a.dim, vd = a.vdim > 0 ? a.vdim : a.dim, HD = a.H * a.dim, HDv = a.H * vd;
   const int r0 = a.qsl[b], r1 = a.qsl[b + 1];
   if (r0 >= r1) return;
-  const bool on = j < dim;
+  const bool onk = j < dim, on = j < vd;            // this thread's key channel (operands) and value column (state, output)
   const bool fresh = a.positions[r0] == 0;
-  float* Sg = a.state + (int64_t)a.slots[b] * a.slot_stride + a.d + (int64_t)h * dim * dim;
+  const bool after = a.read_after;
+  float* Sg = a.state + (int64_t)a.slots[b] * a.slot_stride + a.d + (int64_t)h * dim * vd;
   float S[MAXD];
 #pragma unroll
-  for (int i = 0; i < MAXD; ++i) S[i] = (i < dim && on && !fresh) ? Sg[(int64_t)i * dim + j] : 0.f;
-  us[j] = on ? a.u[h * dim + j] : 0.f;
+  for (int i = 0; i < MAXD; ++i) S[i] = (i < dim && on && !fresh) ? Sg[(int64_t)i * vd + j] : 0.f;
+  us[j] = (onk && a.u) ? a.u[h * dim + j] : 0.f;
   const E *rp = (const E*)a.r, *kp = (const E*)a.k, *vp = (const E*)a.v;
   float rn = 0.f, kn = 0.f, wn = 0.f, vn = 0.f;
   auto fetch = [&](int t) {
-    if (on) {
+    if (onk) {
       const int64_t o = (int64_t)t * a.ld + h * dim + j;
-      rn = ldf(rp + o); kn = ldf(kp + o); vn = ldf(vp + o);
+      rn = ldf(rp + o) * a.r_scale; kn = ldf(kp + o);
       wn = a.decay_pre[(int64_t)t * HD + h * dim + j];
     }
+    if (on) vn = ldf(vp + (int64_t)t * a.ld + h * vd + j);
   };
   fetch(r0);
   for (int t = r0; t < r1; ++t) {
     const int p = (t - r0) & 1;
-    rs[p][j] = rn; ks[p][j] = kn; ws[p][j] = expf(-expf(wn));
+    rs[p][j] = rn; ks[p][j] = kn; ws[p][j] = expf(log_decay(wn, a.decay_mode, a.tau));
     const float v = vn;
     if (t + 1 < r1) fetch(t + 1);
     __syncthreads();
@@ -129,17 +138,24 @@ __global__ void __launch_bounds__(MAXD) wkv_scan_kernel(WkvArgs a) {
         const float4 r4 = reinterpret_cast<const float4*>(rs[p])[i4], k4 = reinterpret_cast<const float4*>(ks[p])[i4];
         const float4 w4 = reinterpret_cast<const float4*>(ws[p])[i4], u4 = reinterpret_cast<const float4*>(us)[i4];
         float kv;
+        if (after) {                                 // the read-out sees the state after this token's update
+          S[i4 * 4 + 0] = fmaf(w4.x, S[i4 * 4 + 0], k4.x * v); acc0 = fmaf(r4.x, S[i4 * 4 + 0], acc0);
+          S[i4 * 4 + 1] = fmaf(w4.y, S[i4 * 4 + 1], k4.y * v); acc1 = fmaf(r4.y, S[i4 * 4 + 1], acc1);
+          S[i4 * 4 + 2] = fmaf(w4.z, S[i4 * 4 + 2], k4.z * v); acc2 = fmaf(r4.z, S[i4 * 4 + 2], acc2);
+          S[i4 * 4 + 3] = fmaf(w4.w, S[i4 * 4 + 3], k4.w * v); acc3 = fmaf(r4.w, S[i4 * 4 + 3], acc3);
+        } else {
         kv = k4.x * v; acc0 = fmaf(r4.x, fmaf(u4.x, kv, S[i4 * 4 + 0]), acc0); S[i4 * 4 + 0] = fmaf(w4.x, S[i4 * 4 + 0], kv);
         kv = k4.y * v; acc1 = fmaf(r4.y, fmaf(u4.y, kv, S[i4 * 4 + 1]), acc1); S[i4 * 4 + 1] = fmaf(w4.y, S[i4 * 4 + 1], kv);
         kv = k4.z * v; acc2 = fmaf(r4.z, fmaf(u4.z, kv, S[i4 * 4 + 2]), acc2); S[i4 * 4 + 2] = fmaf(w4.z, S[i4 * 4 + 2], kv);
         kv = k4.w * v; acc3 = fmaf(r4.w, fmaf(u4.w, kv, S[i4 * 4 + 3]), acc3); S[i4 * 4 + 3] = fmaf(w4.w, S[i4 * 4 + 3], kv);
+        }
       }
     }
-    if (on) a.o32[(int64_t)t * HD + h * dim + j] = (acc0 + acc1) + (acc2 + acc3);
+    if (on) a.o32[(int64_t)t * HDv + h * vd + j] = (acc0 + acc1) + (acc2 + acc3);
   }
   if (on) {
 #pragma unroll
-    for (int i = 0; i < MAXD; ++i) if (i < dim) Sg[(int64_t)i * dim + j] = S[i];
+    for (int i = 0; i < MAXD; ++i) if (i < dim) Sg[(int64_t)i * vd + j] = S[i];
   }
 }
 
@@ -169,11 +185,12 @@ __global__ void __launch_bounds__(256) wkv_chunk_kernel(WkvArgs a) {
   float* Ss = PT + WC * WLC;            // [WD][WLD] the state at the chunk's start
   float* us = Ss + WD * WLD;            // [WD] bonus
   float* el = us + WD;                  // [WD] e^{L_last}
-  const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, dim = a.dim, HD = a.H * a.dim;
+  const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, dim = a.dim, vd = a.vdim > 0 ? a.vdim : a.dim, HD = a.H * a.dim, HDv = a.H * vd;
   const int r0 = a.qsl[b], r1 = a.qsl[b + 1];
   if (r0 >= r1) return;
   const bool fresh = a.positions[r0] == 0;
-  float* Sg = a.state + (int64_t)a.slots[b] * a.slot_stride + a.d + (int64_t)h * dim * dim;
+  const int inc = a.read_after ? 1 : 0;            // 1: token t reads the state after its own update (L_t in place of L_(t-1), no bonus)
+  float* Sg = a.state + (int64_t)a.slots[b] * a.slot_stride + a.d + (int64_t)h * dim * vd;
   const int kg = tid >> 4, vg = tid & 15;          // this thread's state tile: rows kg * 4 .., columns vg * 4 ..
   float S[4][4];
 #pragma unroll
@@ -181,9 +198,9 @@ __global__ void __launch_bounds__(256) wkv_chunk_kernel(WkvArgs a) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int k = kg * 4 + i, v = vg * 4 + j;
-      S[i][j] = (!fresh && k < dim && v < dim) ? Sg[(int64_t)k * dim + v] : 0.f;
+      S[i][j] = (!fresh && k < dim && v < vd) ? Sg[(int64_t)k * vd + v] : 0.f;
     }
-  if (tid < WD) us[tid] = tid < dim ? a.u[h * dim + tid] : 0.f;
+  if (tid < WD) us[tid] = (tid < dim && a.u) ? a.u[h * dim + tid] : 0.f;
   const E *rp = (const E*)a.r, *kp = (const E*)a.k, *vp = (const E*)a.v;
   for (int c0 = r0; c0 < r1; c0 += WC) {
     const int n = min(WC, r1 - c0);
@@ -192,10 +209,10 @@ __global__ void __launch_bounds__(256) wkv_chunk_kernel(WkvArgs a) {
       const int t = i / WD, c = i % WD;
       const bool ok = t < n && c < dim;
       const int64_t o = (int64_t)(c0 + t) * a.ld + h * dim + c;
-      rs[t * WLD + c] = ok ? ldf(rp + o) : 0.f;
+      rs[t * WLD + c] = ok ? ldf(rp + o) * a.r_scale : 0.f;
       ks[t * WLD + c] = ok ? ldf(kp + o) : 0.f;
-      vs[t * WLD + c] = ok ? ldf(vp + o) : 0.f;
-      Ls[t * WLD + c] = ok ? -expf(a.decay_pre[(int64_t)(c0 + t) * HD + h * dim + c]) * 1.4426950408889634f : 0.f;
+      vs[t * WLD + c] = (t < n && c < vd) ? ldf(vp + (int64_t)(c0 + t) * a.ld + h * vd + c) : 0.f;
+      Ls[t * WLD + c] = ok ? log_decay(a.decay_pre[(int64_t)(c0 + t) * HD + h * dim + c], a.decay_mode, a.tau) * 1.4426950408889634f : 0.f;
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(Ss + (kg * 4 + i) * WLD + vg * 4) = make_float4(S[i][0], S[i][1], S[i][2], S[i][3]);
@@ -209,7 +226,7 @@ __global__ void __launch_bounds__(256) wkv_chunk_kernel(WkvArgs a) {
     __syncthreads();
     for (int i = tid; i < WC * WD; i += 256) {
       const int t = i / WD, c = i % WD;
-      const float lm1 = t > 0 ? Ls[(t - 1) * WLD + c] : 0.f;
+      const float lm1 = t + inc > 0 ? Ls[(t - 1 + inc) * WLD + c] : 0.f;
       rdT[c * WLC + t] = rs[t * WLD + c] * exp2f(lm1);
       kd[t * WLD + c] = ks[t * WLD + c] * exp2f(Ls[(WC - 1) * WLD + c] - Ls[t * WLD + c]);
     }
@@ -217,10 +234,10 @@ __global__ void __launch_bounds__(256) wkv_chunk_kernel(WkvArgs a) {
       // scores: thread (t, j mod 8) walks its keys j <= t
       const int t = tid >> 3, jq = tid & 7;
       const float* rt = rs + t * WLD;
-      const float* lt = Ls + (t - 1) * WLD;        // read only for j < t, so t >= 1
+      const float* lt = Ls + (t - 1 + inc) * WLD;  // read only for j < t + inc, so the row exists
       for (int j = jq; j < WC; j += 8) {
         float acc = 0.f;
-        if (j < t) {
+        if (j < t + inc) {
           const float *kj = ks + j * WLD, *lj = Ls + j * WLD;
 #pragma unroll 4
           for (int c = 0; c < WD; c += 4) {
@@ -262,7 +279,7 @@ __global__ void __launch_bounds__(256) wkv_chunk_kernel(WkvArgs a) {
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         const int t = tg * 2 + i;
-        if (t < n && vg * 4 < dim) *reinterpret_cast<float4*>(a.o32 + (int64_t)(c0 + t) * HD + h * dim + vg * 4) = make_float4(o[i][0], o[i][1], o[i][2], o[i][3]);
+        if (t < n && vg * 4 < vd) *reinterpret_cast<float4*>(a.o32 + (int64_t)(c0 + t) * HDv + h * vd + vg * 4) = make_float4(o[i][0], o[i][1], o[i][2], o[i][3]);
       }
     }
     {
@@ -290,7 +307,7 @@ __global__ void __launch_bounds__(256) wkv_chunk_kernel(WkvArgs a) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int k = kg * 4 + i, v = vg * 4 + j;
-      if (k < dim && v < dim) Sg[(int64_t)k * dim + v] = S[i][j];
+      if (k < dim && v < vd) Sg[(int64_t)k * vd + v] = S[i][j];
     }
 }
 
@@ -301,7 +318,7 @@ __global__ void __launch_bounds__(256) wkv_norm_gate_kernel(WkvArgs a) {
   pdl_wait();
   const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (item >= (int64_t)a.T * a.H) return;
-  const int lane = threadIdx.x & 31, t = (int)(item / a.H), h = (int)(item % a.H), dim = a.dim, HD = a.H * a.dim;
+  const int lane = threadIdx.x & 31, t = (int)(item / a.H), h = (int)(item % a.H), dim = a.vdim > 0 ? a.vdim : a.dim, HD = a.H * dim;
   const float* o = a.o32 + (int64_t)t * HD + h * dim;
   float ss = 0.f;
   for (int c = lane; c < dim; c += 32) ss = fmaf(o[c], o[c], ss);
@@ -319,7 +336,8 @@ static int wkv_scan_t(const WkvArgs& a, cudaStream_t st) {
   const dim3 grid(a.B, a.H);
   cudaError_t ce;
   // requests with many rows: 32 tokens at a time (the o32 rows are 16-byte aligned when the head size is a multiple of 4)
-  if (a.max_q >= 8 && a.dim <= WD && a.dim % 4 == 0) {
+  const int vd = a.vdim > 0 ? a.vdim : a.dim, md = std::max(a.dim, vd);
+  if (a.max_q >= 8 && a.dim <= WD && a.dim % 4 == 0 && vd <= WD && vd % 4 == 0 && a.H * vd % 4 == 0) {
     static bool smem_set = false;
     if (!smem_set) {
       KGE_CUDA_OK(cudaFuncSetAttribute(wkv_chunk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WKV_CHUNK_SMEM));
@@ -327,9 +345,9 @@ static int wkv_scan_t(const WkvArgs& a, cudaStream_t st) {
       smem_set = true;
     }
     ce = launch_pdl(wkv_chunk_kernel<E>, grid, dim3(256), WKV_CHUNK_SMEM, st, a);
-  } else if (a.dim <= 32) ce = launch_pdl(wkv_scan_kernel<E, 32>, grid, dim3(32), 0, st, a);
-  else if (a.dim <= 64) ce = launch_pdl(wkv_scan_kernel<E, 64>, grid, dim3(64), 0, st, a);
-  else if (a.dim <= 128) ce = launch_pdl(wkv_scan_kernel<E, 128>, grid, dim3(128), 0, st, a);
+  } else if (md <= 32) ce = launch_pdl(wkv_scan_kernel<E, 32>, grid, dim3(32), 0, st, a);
+  else if (md <= 64) ce = launch_pdl(wkv_scan_kernel<E, 64>, grid, dim3(64), 0, st, a);
+  else if (md <= 128) ce = launch_pdl(wkv_scan_kernel<E, 128>, grid, dim3(128), 0, st, a);
   else ce = launch_pdl(wkv_scan_kernel<E, 256>, grid, dim3(256), 0, st, a);
   KGE_CUDA_OK(ce);
   const int64_t items = (int64_t)a.T * a.H;
@@ -339,7 +357,8 @@ static int wkv_scan_t(const WkvArgs& a, cudaStream_t st) {
 
 int wkv_scan(const WkvArgs& a, cudaStream_t st) {
   if (a.T <= 0) return 0;
-  KGE_REQUIRE(a.dim > 0 && a.dim <= 256 && a.B <= 65535 * 32 && a.H <= 65535, "wkv_scan: head size %d (1 .. 256)", a.dim);
+  KGE_REQUIRE(a.dim > 0 && a.dim <= 256 && a.vdim >= 0 && a.vdim <= 256 && a.B <= 65535 * 32 && a.H <= 65535, "wkv_scan: head size %d x %d (1 .. 256)", a.dim, a.vdim);
+  KGE_REQUIRE(a.u || a.read_after, "wkv_scan: the read-out before the update needs the bonus vector");
   return a.elt == KGE_ELT_F32 ? wkv_scan_t<float>(a, st) : wkv_scan_t<__nv_bfloat16>(a, st);
 }
 
