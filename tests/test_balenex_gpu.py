@@ -1,0 +1,469 @@
+"""The Balenex design in the engine against the plain float64 oracle (oracle/balenex.py): every mechanism alone, whole
+prompts against pieces and token-by-token decoding, mixed batches, reused pages and state slots, keys just inside and
+just outside every window, kept first tokens and pooled blocks at their edges (scores peaked so that one key decides),
+slowly decaying recurrent memory, the first tokens, long decoding, other sizes, and greedy generation through the
+scheduler.  float32 engines give the sharp comparison; bfloat16 ones are held to a rounding-sized bound."""
+import copy
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import balenex as ob
+
+pytestmark = pytest.mark.gpu
+
+
+def make_engine(kge, tmp_path, cfg, W, dtype="float32", tokens=512, bs=16, seqs=4, name="m", batched=0):
+    d = str(tmp_path / name)
+    ob.save_model_dir(d, cfg, W)
+    nb = (tokens + bs - 1) // bs
+    return kge.LLM(d, dtype=dtype, block_size=bs, num_gpu_blocks_override=nb + 1, max_model_len=nb * bs + 1, max_num_seqs=seqs,
+                   max_num_batched_tokens=batched or nb * bs, enable_prefix_caching=False)
+
+
+def run_pieces(llm, rid, tokens, pieces):
+    """Feed `tokens` in steps of the given sizes, asking for every position's logits."""
+    out, at = [], 0
+    for n in pieces:
+        llm.trace_add(rid, tokens[at:at + n])
+        out.append(llm.trace_step([(rid, n, list(range(n)))]))
+        at += n
+    assert at == len(tokens)
+    return np.concatenate(out)
+
+
+def check(got, want, dtype, what="", noise=None, f32=2e-4):
+    """Row-wise error against the oracle, relative to the logits' size.  float32 engines are held to 2e-4.  bfloat16
+    engines are held to 4e-2, or, where the case gives `noise` (ob.bfloat16_noise: what rounding alone does in the oracle,
+    per row), to three times the noise that nine rows in ten stay below; one row in ten may pass that bound, up to three
+    times the noisiest row of the oracle."""
+    want = want.numpy() if isinstance(want, torch.Tensor) else want
+    scale = np.sqrt((want ** 2).mean())
+    err = np.sqrt(((got - want) ** 2).mean(-1)) / scale
+    lim = f32 if dtype == "float32" else (max(4e-2, 3.0 * float(np.quantile(noise, 0.9))) if noise is not None else 4e-2)
+    over = err >= lim
+    worst = int(np.argmax(err))
+    if dtype != "float32" and noise is not None and over.any():
+        assert over.mean() <= 0.1 and (err[over] < 3.0 * float(np.max(noise))).all(), \
+            f"{what}: {over.sum()} of {len(err)} rows over {lim:.3g}, row {worst} is {err[worst]:.3g} of the logits' size"
+        return
+    assert not over.any(), f"{what}: row {worst} is {err[worst]:.3g} of the logits' size (limit {lim:.3g})"
+
+
+def prompt(cfg, n, seed=1):
+    return torch.randint(0, cfg["vocab"], (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def silence(W, *ends):
+    for k in W:
+        if k.endswith(ends):
+            W[k] = torch.zeros_like(W[k])
+    return W
+
+
+ALONE = {
+    # one side of the parallel mixer at a time (the other side's output matrix is zero: its normed output is zero too)
+    "window": (dict(layers=[ob.parallel_layer(ff=0)]), ("right.o",)),
+    "window-no-kept-tokens": (dict(layers=[ob.parallel_layer(keep_first=0, ff=0)]), ("right.o",)),
+    "window-kept-beyond-window": (dict(layers=[ob.parallel_layer(size=3, keep_first=6, ff=0)]), ("right.o",)),
+    "window-no-rotation": (dict(layers=[ob.parallel_layer(rot_dims=0, ff=0)]), ("right.o",)),
+    "window-all-dims-rotate": (dict(layers=[ob.parallel_layer(rot_dims=8, ff=0)]), ("right.o",)),
+    "window-no-conv": (dict(layers=[ob.parallel_layer(conv=1, ff=0)]), ("right.o",)),
+    "window-four-taps": (dict(layers=[ob.parallel_layer(conv=4, ff=0)]), ("right.o",)),
+    "window-one-kv-head": (dict(layers=[ob.parallel_layer(heads=3, kv_heads=1, ff=0)]), ("right.o",)),
+    "window-every-head-its-kv": (dict(layers=[ob.parallel_layer(heads=2, kv_heads=2, ff=0)]), ("right.o",)),
+    "gla": (dict(layers=[ob.parallel_layer(ff=0)]), ("left.o",)),
+    "gla-one-head": (dict(layers=[ob.parallel_layer(r_heads=1, r_dim=12, r_vdim=4, tau=1.0, ff=0)]), ("left.o",)),
+    "both-sides": (dict(layers=[ob.parallel_layer(ff=0)]), ()),
+    "pooled": (dict(layers=[ob.attention_layer(ff=0)]), ()),
+    "pooled-blocks-of-one": (dict(layers=[ob.attention_layer(pool=1, ff=0)]), ()),
+    "pooled-block-wider-than-window": (dict(layers=[ob.attention_layer(size=3, pool=5, ff=0)]), ()),
+    "pooled-block-wider-than-page": (dict(layers=[ob.attention_layer(size=4, pool=19, ff=0)]), ()),
+    "pooled-one-kv-head": (dict(layers=[ob.attention_layer(heads=3, kv_heads=1, ff=0)]), ()),
+    "dense": (dict(layers=[ob.attention_layer()]), ("mix.o", "mix.o.b")),
+    "one-norm-group": (dict(layers=[ob.attention_layer()], groups=1), ()),
+    "every-column-its-group": (dict(layers=[ob.parallel_layer()], groups=24), ()),
+}
+
+
+@pytest.mark.parametrize("mech", sorted(ALONE))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mechanism_alone(kge, tmp_path, mech, dtype):
+    kw, off = ALONE[mech]
+    cfg = ob.make_config(**kw)
+    W = silence(ob.make_weights(cfg, seed=3), *off) if off else ob.make_weights(cfg, seed=3)
+    toks = prompt(cfg, 45)
+    want = ob.forward(cfg, W, toks)
+    llm = make_engine(kge, tmp_path, cfg, W, dtype)
+    got = run_pieces(llm, 0, toks, [45])
+    llm.close()
+    check(got, want, dtype, mech, ob.bfloat16_noise(cfg, W, toks))
+
+
+def full(**kw):
+    """Both kinds of layer with different windows, kept tokens, pools, heads and taps, a layer without feed-forward."""
+    layers = [ob.parallel_layer(), ob.attention_layer(), ob.attention_layer(heads=2, kv_heads=1, dim=6, vdim=10, size=11, pool=4, scale=0.3, ff=0),
+              ob.parallel_layer(heads=3, kv_heads=3, dim=6, vdim=4, conv=2, size=9, keep_first=3, rot_dims=6, base=30.0, r_heads=3, r_dim=4, r_vdim=4, tau=9.0, ff=16)]
+    return ob.make_config(layers, **kw)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prefill_decode_and_pieces_agree_with_the_oracle(kge, tmp_path, dtype):
+    cfg = full()
+    W = ob.make_weights(cfg, seed=5)
+    toks = prompt(cfg, 75)
+    want = ob.forward(cfg, W, toks)
+    noise = ob.bfloat16_noise(cfg, W, toks)
+    llm = make_engine(kge, tmp_path, cfg, W, dtype)
+    for rid, pieces in enumerate([[75], [30] + [1] * 45, [1] * 75, [2, 3, 17, 2, 31, 5, 2, 2, 9, 2], [23, 2, 24, 26], [47, 2, 1, 1, 24]]):
+        got = run_pieces(llm, rid, toks, pieces)
+        llm.trace_end(rid)
+        check(got, want, dtype, f"pieces {pieces[:6]}", noise)
+    llm.close()
+
+
+def test_layer_outputs_match(kge, tmp_path):
+    """The residual stream after every layer."""
+    cfg = full()
+    W = ob.make_weights(cfg, seed=6)
+    toks = prompt(cfg, 33)
+    _, layers = ob.forward(cfg, W, toks, return_layers=True)
+    llm = make_engine(kge, tmp_path, cfg, W, "float32")
+    buf = np.zeros((4, 33, cfg["width"]), dtype=np.float32)
+    llm.set_layer_dump(buf)
+    run_pieces(llm, 0, toks, [20, 13])
+    last = buf.reshape(-1)[:4 * 13 * cfg["width"]].reshape(4, 13, cfg["width"]).copy()      # the dump is packed per step: [layer, row of the step, width]
+    llm.set_layer_dump(None)
+    llm.close()
+    for i, x in enumerate(layers):      # the dump holds the last step's rows: positions 20 .. 32
+        assert np.abs(last[i] - x.numpy()[20:]).max() < 2e-4 * float(x.abs().max()), f"layer {i}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_batches_of_unequal_requests(kge, tmp_path, dtype):
+    cfg = full()
+    W = ob.make_weights(cfg, seed=7)
+    P = {0: prompt(cfg, 61, 10), 1: prompt(cfg, 9, 11), 2: prompt(cfg, 40, 12), 3: prompt(cfg, 1, 13)}
+    want = {r: ob.forward(cfg, W, t).numpy() for r, t in P.items()}
+    # each step: (request, number of tokens); prompt pieces beside single tokens, requests pausing and resuming
+    steps = [[(0, 19), (1, 1), (3, 1)], [(1, 1), (2, 2), (0, 2)], [(0, 20), (1, 1)], [(2, 18), (1, 1), (0, 1)], [(1, 5), (2, 1)],
+             [(0, 1), (2, 1)], [(0, 18), (2, 18)]]
+    llm = make_engine(kge, tmp_path, cfg, W, dtype)
+    at = {r: 0 for r in P}
+    got = {r: [] for r in P}
+    for st in steps:
+        entries = []
+        for r, n in st:
+            llm.trace_add(r, P[r][at[r]:at[r] + n])
+            entries.append((r, n, list(range(n))))
+        lg = llm.trace_step(entries)
+        k = 0
+        for r, n in st:
+            got[r].append(lg[k:k + n])
+            k += n
+            at[r] += n
+    llm.close()
+    for r in P:
+        assert at[r] == len(P[r])
+        check(np.concatenate(got[r]), want[r], dtype, f"request {r}", ob.bfloat16_noise(cfg, W, P[r]))
+
+
+def test_pages_and_slots_are_used_again(kge, tmp_path):
+    """Two state slots and a pool of 96 tokens: five requests pass through, each in pages and a slot that an earlier
+    request filled; each must come out as if it had run alone (a slot's old matrix or convolution rows, or a page's
+    old pooled entries, must not leak)."""
+    cfg = full()
+    W = ob.make_weights(cfg, seed=8)
+    llm = make_engine(kge, tmp_path, cfg, W, "float32", tokens=96, bs=16, seqs=2)
+    P = {r: prompt(cfg, n, 20 + r) for r, n in enumerate([40, 33, 47, 18, 30])}
+    want = {r: ob.forward(cfg, W, t).numpy() for r, t in P.items()}
+    got = {}
+    got[0] = run_pieces(llm, 0, P[0], [40])
+    llm.trace_add(1, P[1][:20])
+    a = llm.trace_step([(1, 20, list(range(20)))])
+    llm.trace_end(0)
+    llm.trace_add(2, P[2])
+    llm.trace_add(1, P[1][20:])
+    b = llm.trace_step([(2, 30, list(range(30))), (1, 13, list(range(13)))])
+    got[1] = np.concatenate([a, b[30:]])
+    c = llm.trace_step([(2, 17, list(range(17)))])
+    got[2] = np.concatenate([b[:30], c])
+    llm.trace_end(1)
+    got[3] = run_pieces(llm, 3, P[3], [2, 16])
+    llm.trace_end(2)
+    llm.trace_end(3)
+    got[4] = run_pieces(llm, 4, P[4], [29, 1])
+    llm.close()
+    for r in P:
+        check(got[r], want[r], "float32", f"request {r}")
+
+
+def edge_case(kind, dim, vdim, size, extra):
+    """One attention mechanism alone with a large score scale, so that single keys (or single pooled blocks) carry most
+    of a row's weight: a window that is one token off, a kept token or a pooled block seen one step early or late, moves
+    the logits far beyond rounding."""
+    if kind == "window":
+        L = ob.parallel_layer(heads=4, kv_heads=2, dim=dim, vdim=vdim, size=size, keep_first=extra, rot_dims=dim // 2, base=500.0, scale=10.0 / dim, conv=3, ff=0)
+    else:
+        L = ob.attention_layer(heads=4, kv_heads=2, dim=dim, vdim=vdim, size=size, pool=extra, scale=10.0 / dim, ff=0)
+    return ob.make_config([L], width=32, groups=2)
+
+
+def edge_prompt(cfg, kind, pool):
+    """Random tokens; for pooled blocks, runs of one token that fill a block each: the layer has no positions, so the
+    block's mean key is that token's key at full length and a block weighs as much as a token."""
+    if kind == "window":
+        return prompt(cfg, 200, 30)
+    base = prompt(cfg, 200, 30)
+    return [base[j // pool] for j in range(200)]
+
+
+EDGES = [("window", 8, 6, 21, 3), ("window", 16, 16, 37, 5), ("pooled", 8, 6, 21, 4), ("pooled", 16, 24, 37, 7), ("pooled", 32, 32, 70, 16)]
+
+
+@pytest.mark.parametrize("case", EDGES)      # head sizes for the per-row kernel and (bfloat16, multiples of 16) the tensor-core kernel
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_window_edges_kept_tokens_and_pooled_blocks_with_peaked_scores(kge, tmp_path, dtype, case):
+    kind, dim, vdim, size, extra = case
+    cfg = edge_case(*case)
+    W = ob.make_weights(cfg, seed=9)
+    if kind == "window":
+        silence(W, "right.o")
+    toks = edge_prompt(cfg, kind, extra)
+    want = ob.forward(cfg, W, toks)
+    # the setup shows what it should: a window one token wider or narrower, one kept token / one position of pooling more or less,
+    # each move a good part of the late rows visibly
+    scale = float(want.pow(2).mean().sqrt())
+    for key, sub, delta in [("size", None, 1), ("size", None, -1), ("keep_first" if kind == "window" else "pool", None, 1), ("keep_first" if kind == "window" else "pool", None, -1)]:
+        other = copy.deepcopy(cfg)
+        m = other["layers"][0]["mixer"]
+        m = m["left"] if kind == "window" else m
+        m["mask"][key] += delta
+        diff = (ob.forward(other, W, toks) - want)[size + 8:].pow(2).mean(-1).sqrt() / scale
+        assert float((diff > 0.02).to(torch.float64).mean()) > 0.05 and float(diff.max()) > 0.05, f"{key} {delta:+d} does not show"
+    llm = make_engine(kge, tmp_path, cfg, W, dtype, bs=16)
+    noise = ob.bfloat16_noise(cfg, W, toks)
+    check(run_pieces(llm, 0, toks, [200]), want, dtype, "whole", noise)
+    llm.trace_end(0)
+    check(run_pieces(llm, 1, toks[:100], [15, 1, 1, 1, 14, 2, 30, 1, 1, 34]), want[:100], dtype, "pieces and single tokens across page borders", noise[:100])
+    llm.trace_end(1)
+    got = np.concatenate([run_pieces(llm, 2, toks[:size - 2], [size - 2]), run_pieces(llm, 2, toks[size - 2:], [1] * (200 - size + 2))])
+    check(got, want, dtype, "decoding while the window, the kept tokens and the pooled blocks come into play", noise)
+    llm.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_far_kept_token_decides(kge, tmp_path, dtype):
+    """A kept first token whose key is made to stand out: hundreds of positions later most of every row's weight still
+    sits on it, at its true position (the rotation of its key and of its value must be that of position 1)."""
+    cfg = edge_case("window", 16, 16, 20, 2)
+    W = silence(ob.make_weights(cfg, seed=16), "right.o")
+    toks = prompt(cfg, 300, 33)
+    x = W["embed"][torch.tensor(toks)]
+    h = ob.group_norm(x, W["l0.norm1"], 2, cfg["norm"]["eps"])
+    m = cfg["layers"][0]["mixer"]["left"]
+    q, k, _ = ob.left_qkv(h, ob.sub(W, "l0.mix.left."), m, cfg["norm"]["eps"])
+    w = ob.left_weights(q, k, m, 0)
+    assert float(w[250:, :2].sum(-1).mean()) > 0.05      # the kept tokens carry real weight far away
+    want = ob.forward(cfg, W, toks)
+    moved = ob.forward(cfg, W, toks[:1] + [(toks[1] + 1) % cfg["vocab"]] + toks[2:])
+    assert float((moved - want)[250:].abs().max()) > 0.05
+    llm = make_engine(kge, tmp_path, cfg, W, dtype, bs=16)
+    noise = ob.bfloat16_noise(cfg, W, toks)
+    check(run_pieces(llm, 0, toks, [300]), want, dtype, "whole", noise)
+    llm.trace_end(0)
+    got = np.concatenate([run_pieces(llm, 1, toks[:270], [100, 3, 167]), run_pieces(llm, 1, toks[270:], [1] * 30)])
+    check(got, want, dtype, "pieces, then decoding", noise)
+    llm.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_recurrent_memory_that_decays_slowly(kge, tmp_path, dtype):
+    """Gated linear attention alone with decays close to 1 (and a few fast channels): the matrix state remembers the first
+    tokens for hundreds of positions, so a state that is lost, reset or carried over at the cut of a prompt shows at the end."""
+    cfg = ob.make_config([ob.parallel_layer(r_heads=2, r_dim=16, r_vdim=12, tau=16.0, ff=0)], width=32, groups=4)
+    W = silence(ob.make_weights(cfg, seed=10), "left.o")
+    W["l0.mix.right.a2.b"] = torch.where(torch.arange(32) % 5 == 0, -1.0, 5.0).to(ob.DT)
+    W["l0.mix.right.a2"] = W["l0.mix.right.a2"] * 0.25
+    toks = prompt(cfg, 260, 31)
+    want = ob.forward(cfg, W, toks)
+    other = ob.forward(cfg, W, prompt(cfg, 8, 32) + toks[8:])
+    assert float((other[-20:] - want[-20:]).abs().max()) > 0.05      # the first tokens still matter 250 positions later
+    llm = make_engine(kge, tmp_path, cfg, W, dtype)
+    noise = ob.bfloat16_noise(cfg, W, toks)
+    check(run_pieces(llm, 0, toks, [260]), want, dtype, "whole", noise)
+    llm.trace_end(0)
+    check(run_pieces(llm, 1, toks, [63, 2, 1, 64, 2, 97, 1, 30]), want, dtype, "pieces", noise)
+    llm.trace_end(1)
+    check(run_pieces(llm, 2, toks, [200] + [1] * 60), want, dtype, "decoding", noise)
+    llm.close()
+
+
+def test_convolution_rows_cross_every_cut(kge, tmp_path):
+    """Four taps: the three projected rows before a step's first token come from the slot, also when the steps before
+    brought one or two tokens only."""
+    cfg = ob.make_config([ob.parallel_layer(conv=4, ff=0), ob.parallel_layer(conv=2, size=5, ff=0)])
+    W = ob.make_weights(cfg, seed=22)
+    toks = prompt(cfg, 40, 36)
+    want = ob.forward(cfg, W, toks)
+    llm = make_engine(kge, tmp_path, cfg, W, "float32")
+    for rid, pieces in enumerate([[1, 1, 2, 1, 3, 2, 30], [2, 1, 1, 1, 1, 34], [5, 1, 2, 32]]):
+        check(run_pieces(llm, rid, toks, pieces), want, "float32", f"pieces {pieces}")
+        llm.trace_end(rid)
+    llm.close()
+
+
+def test_tensor_core_sizes(kge, tmp_path):
+    """bfloat16 at sizes the tensor-core paths take: 16-byte rows everywhere, key sizes that are multiples of 16,
+    64-token pages, prompts long enough for the 64-row attention CTAs and the chunked recurrence, windows that end inside
+    a key tile, kept tokens and pooled blocks that fill more than one tile."""
+    layers = [ob.parallel_layer(heads=4, kv_heads=2, dim=32, vdim=16, size=70, keep_first=40, rot_dims=16, base=1000.0, scale=0.25, r_heads=2, r_dim=32, r_vdim=64, tau=8.0, ff=128),
+              ob.attention_layer(heads=6, kv_heads=2, dim=16, vdim=32, size=45, pool=2, scale=0.3, ff=64),
+              ob.parallel_layer(heads=2, kv_heads=1, dim=64, vdim=64, size=33, keep_first=1, rot_dims=64, scale=0.2, r_heads=1, r_dim=64, r_vdim=32, tau=3.0, ff=64)]
+    cfg = ob.make_config(layers, width=64, groups=4, vocab=96)
+    W = ob.make_weights(cfg, seed=15, decay_rank=8)
+    toks = prompt(cfg, 290, 32)
+    want = ob.forward(cfg, W, toks)
+    noise = ob.bfloat16_noise(cfg, W, toks)
+    llm = make_engine(kge, tmp_path, cfg, W, "bfloat16", bs=64, tokens=1024)
+    check(run_pieces(llm, 0, toks, [290]), want, "bfloat16", "whole", noise)
+    llm.trace_end(0)
+    got = np.concatenate([run_pieces(llm, 1, toks[:150], [150]), run_pieces(llm, 1, toks[150:260], [3, 45, 2, 60]), run_pieces(llm, 1, toks[260:], [1] * 30)])
+    check(got, want, "bfloat16", "pieces, then decoding", noise)
+    llm.trace_end(1)
+    # two requests decoding side by side (one far longer than the other), then single tokens beside a prompt piece
+    a, b = prompt(cfg, 150, 35), prompt(cfg, 9, 36)
+    wa, wb = ob.forward(cfg, W, a).numpy(), ob.forward(cfg, W, b).numpy()
+    llm.trace_add(2, a[:140])
+    llm.trace_add(3, b[:3])
+    llm.trace_step([(2, 140, []), (3, 3, [])])
+    ga, gb = [], []
+    for i in range(6):
+        llm.trace_add(2, a[140 + i:141 + i])
+        llm.trace_add(3, b[3 + i:4 + i])
+        lg = llm.trace_step([(2, 1, [0]), (3, 1, [0])])
+        ga.append(lg[0])
+        gb.append(lg[1])
+    c = prompt(cfg, 70, 37)
+    llm.trace_end(3)
+    llm.trace_add(2, a[146:147])
+    llm.trace_add(4, c[:66])
+    lg = llm.trace_step([(2, 1, [0]), (4, 66, list(range(66)))])
+    llm.close()
+    check(np.stack(ga), wa[140:146], "bfloat16", "long request of a decode batch", noise)
+    check(np.stack(gb), wb[3:9], "bfloat16", "short request of a decode batch", noise)
+    check(lg[:1], wa[146:147], "bfloat16", "a single token beside a prompt piece", noise)
+    check(lg[1:], ob.forward(cfg, W, c).numpy()[:66], "bfloat16", "a prompt piece beside a single token", noise)
+
+
+def test_first_tokens(kge, tmp_path):
+    cfg = full()
+    W = ob.make_weights(cfg, seed=11)
+    llm = make_engine(kge, tmp_path, cfg, W, "float32")
+    for rid, n in enumerate([1, 2, 3, 5]):
+        toks = prompt(cfg, n, 40 + n)
+        got = run_pieces(llm, rid, toks, [n])
+        llm.trace_end(rid)
+        check(got, ob.forward(cfg, W, toks), "float32", f"{n} tokens")
+    llm.close()
+
+
+def test_long_decoding(kge, tmp_path):
+    cfg = full()
+    W = ob.make_weights(cfg, seed=12)
+    toks = prompt(cfg, 200, 50)
+    llm = make_engine(kge, tmp_path, cfg, W, "float32")
+    got = run_pieces(llm, 0, toks, [4] + [1] * 196)
+    llm.close()
+    check(got, ob.forward(cfg, W, toks), "float32")
+
+
+OTHER = [
+    # nothing is 16-byte aligned; one group; a pool that does not divide the page; only pooled layers
+    dict(layers=[ob.attention_layer(heads=3, kv_heads=3, dim=5, vdim=7, size=6, pool=5, ff=7), ob.attention_layer(heads=2, kv_heads=1, dim=9, vdim=3, size=17, pool=3, ff=0)],
+         vocab=53, width=22, groups=1, eps=1e-3),
+    # only parallel layers; a window longer than the prompt; more kept tokens than the window holds; five taps
+    dict(layers=[ob.parallel_layer(heads=5, kv_heads=1, dim=6, vdim=2, conv=5, size=64, keep_first=1, rot_dims=2, r_heads=1, r_dim=7, r_vdim=9, tau=1.0, ff=9),
+                 ob.parallel_layer(heads=2, kv_heads=2, dim=10, vdim=10, conv=1, size=2, keep_first=9, rot_dims=10, base=7.0, r_heads=3, r_dim=5, r_vdim=3, tau=32.0, ff=0)],
+         vocab=67, width=42, groups=7),
+    # a window of one token; equal sizes everywhere; recurrence heads wider than a warp and wider than the chunked kernel takes
+    dict(layers=[ob.attention_layer(heads=2, kv_heads=2, dim=8, vdim=8, size=1, pool=8, ff=8), ob.parallel_layer(heads=2, kv_heads=2, dim=8, vdim=8, conv=2, size=8, keep_first=8, rot_dims=8, r_heads=1, r_dim=40, r_vdim=72, tau=2.0, ff=8)],
+         vocab=80, width=40, groups=5),
+    # wide value heads, a recurrence whose keys are wider than its values
+    dict(layers=[ob.parallel_layer(heads=2, kv_heads=1, dim=16, vdim=136, size=12, keep_first=2, rot_dims=4, r_heads=2, r_dim=68, r_vdim=8, ff=32), ob.attention_layer(heads=4, kv_heads=1, dim=48, vdim=80, size=9, pool=6, scale=0.2, ff=32)],
+         vocab=90, width=48, groups=3),
+]
+
+
+@pytest.mark.parametrize("sizes", OTHER)
+def test_other_sizes(kge, tmp_path, sizes):
+    cfg = ob.make_config(**sizes)
+    W = ob.make_weights(cfg, seed=13, decay_rank=3)
+    toks = prompt(cfg, 50, 60)
+    want = ob.forward(cfg, W, toks)
+    llm = make_engine(kge, tmp_path, cfg, W, "float32")
+    check(run_pieces(llm, 0, toks, [50]), want, "float32", "whole")
+    check(run_pieces(llm, 1, toks, [13, 2, 1, 1, 1, 32]), want, "float32", "pieces")
+    llm.close()
+    llm = make_engine(kge, tmp_path, cfg, W, "bfloat16", name="b")        # the same sizes through the 16-bit kernels and their fallbacks
+    noise = ob.bfloat16_noise(cfg, W, toks)
+    check(run_pieces(llm, 0, toks, [50]), want, "bfloat16", "whole, bfloat16", noise)
+    check(run_pieces(llm, 1, toks, [13, 2, 1, 1, 1, 32]), want, "bfloat16", "pieces, bfloat16", noise)
+    llm.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_scheduler(kge, tmp_path, dtype):
+    """LLM.generate: the continuous-batching scheduler cuts the prompts into 16-token steps, admits the third request
+    when a slot frees up, samples greedily, and replays its decode steps as a CUDA graph while windows pass over the
+    decoded tokens and pooled blocks fill up."""
+    cfg = full()
+    W = ob.make_weights(cfg, seed=14)
+    prompts = [prompt(cfg, n, 70 + n) for n in (37, 5, 21)]
+    llm = make_engine(kge, tmp_path, cfg, W, dtype, seqs=2, batched=16)
+    outs = llm.generate(prompts, kge.SamplingParams(max_tokens=14, temperature=0.0, ignore_eos=True))
+    assert llm.kernel_launches > 0
+    llm.close()
+    for p, o in zip(prompts, outs):
+        got = o.outputs[0].token_ids
+        assert len(got) == 14
+        toks = list(p)
+        for k, g in enumerate(got):       # teacher-forced: a different choice must be a near-tie of the oracle
+            lg = ob.forward(cfg, W, toks)[-1]
+            best = int(torch.argmax(lg))
+            if g != best:      # the samplers read 16-bit logits rows: two logits within their spacing tie
+                gap = float(lg[best] - lg[g])
+                assert gap < (2.0 ** -7 * max(1.0, float(lg[best].abs())) if dtype == "float32" else 0.15), f"token {k}: chose {g}, oracle {best} leads by {gap}"
+            toks.append(g)
+
+
+def test_trace_runner_command_line(kge, tmp_path):
+    """bin/trace_run end to end on this design: pieces of two requests side by side, a request that ends and one that
+    takes its pages and slot, both number formats."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = full()
+    W = ob.make_weights(cfg, seed=17)
+    d = str(tmp_path / "m")
+    ob.save_model_dir(d, cfg, W)
+    P = {"a": prompt(cfg, 50, 80), "b": prompt(cfg, 31, 81), "c": prompt(cfg, 40, 82)}
+    want = {k: ob.forward(cfg, W, v).numpy() for k, v in P.items()}
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": P["a"][:30], "want": [0, 29]}, {"id": "b", "tokens": P["b"][:2], "want": []}], "end": []},
+        {"step": 1, "entries": [{"id": "b", "tokens": P["b"][2:], "want": [0, 28]}, {"id": "a", "tokens": P["a"][30:31], "want": [0]}], "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": P["a"][31:], "want": [18]}, {"id": "c", "tokens": P["c"], "want": [39, 5]}], "end": ["a", "c"]},
+    ]
+    rows = {0: [("a", 0), ("a", 29)], 1: [("b", 2), ("b", 30), ("a", 30)], 2: [("a", 49), ("c", 39), ("c", 5)]}
+    for dtype in ("float32", "bfloat16"):
+        out = str(tmp_path / ("out_" + dtype))
+        r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", d, "--dtype", dtype, "--out", out, "--max-tokens", "128"],
+                           input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+        for st, rr in rows.items():
+            got = np.fromfile(os.path.join(out, f"{st}.f32"), dtype="<f4").reshape(len(rr), cfg["vocab"])
+            check(got, np.stack([want[k][i] for k, i in rr]), dtype, f"step {st}")
