@@ -2,7 +2,7 @@
 """Headline benchmark: output tokens/s at fixed concurrency (BASELINE.json `metric`).
 
   python bench.py --gpus N --steps K --warmup W [--workload c3|c2|c1] [--impl ours|reference]
-  python bench.py --designs [safupel|girolorn|zezilix]   (a layer-list design beside the closest other model of equal size; one JSON line per size)
+  python bench.py --designs [safupel|girolorn|zezilix|balenex]   (a layer-list design beside the closest other model of equal size; one JSON line per size)
 
 A "step" is one whole job of the workload: every request prefilled (2k-token prompts, 8192 tokens
 per engine step as the continuous-batching scheduler cuts them) and decoded greedily to its output length.
@@ -597,6 +597,30 @@ def zezilix_configs(z):
     return zez, girolorn_configs(GIROLORN_SIZES[z["girolorn"]])[0]
 
 
+BALENEX_SIZES = {
+    # windowed attention beside gated linear attention, and windowed attention over pooled blocks (Balenex), at sizes that
+    # resemble real layers: 128-wide heads, a window of 1024 positions with 4 kept tokens or pooled blocks of 64, linear
+    # attention with 64 x 64 states, a gated feed-forward; the model beside it is the closest one the engine has, the design
+    # with attention and a matrix memory side by side and convolved recurrences (Safupel) of the same width, depth and heads
+    "w2048": dict(width=2048, vocab=32000, reps=2, heads=16, kv=4, dim=128, window=1024, keep=4, pool=64, rot=64, conv=4, r_heads=32, r_dim=64, r_vdim=64,
+                  decay_rank=64, ff=5632, groups=8, safupel="w2048"),
+    "w4096": dict(width=4096, vocab=32000, reps=1, heads=32, kv=8, dim=128, window=1024, keep=4, pool=64, rot=64, conv=4, r_heads=64, r_dim=64, r_vdim=64,
+                  decay_rank=64, ff=11008, groups=8, safupel="w4096"),
+}
+
+
+def balenex_configs(z):
+    left = {"conv": z["conv"], "dim": z["dim"], "heads": z["heads"], "kv_heads": z["kv"], "mask": {"keep_first": z["keep"], "size": z["window"]},
+            "rot": {"base": 10000.0, "dims": z["rot"]}, "scale": z["dim"] ** -0.5, "vdim": z["dim"]}
+    right = {"dim": z["r_dim"], "heads": z["r_heads"], "tau": 16.0, "vdim": z["r_vdim"], "decay_rank": z["decay_rank"]}
+    att = {"dim": z["dim"], "heads": z["heads"], "kv_heads": z["kv"], "mask": {"pool": z["pool"], "size": z["window"]}, "scale": z["dim"] ** -0.5, "vdim": z["dim"]}
+    dense = {"ff": z["ff"], "kind": "dense"}
+    four = [{"mixer": {"left": left, "right": right}, "mlp": dense, "type": "parallel"}, {"mixer": att, "mlp": dense, "type": "attention"},
+            {"mixer": att, "mlp": dense, "type": "attention"}, {"mixer": {"left": left, "right": right}, "mlp": dense, "type": "parallel"}]
+    bal = {"architecture": "Balenex", "layers": four * z["reps"], "norm": {"eps": 1e-6, "groups": z["groups"]}, "vocab": z["vocab"], "width": z["width"]}
+    return bal, design_configs(DESIGN_SIZES[z["safupel"]])[0]
+
+
 def time_raw_steps(kge, llm, batch_np, steps, warmup):
     """Wall-clock seconds per synchronous engine step (metadata upload, kernels, sampled ids back), after warm-up."""
     import ctypes as C
@@ -628,7 +652,7 @@ def raw_batch(B, ctx, q, bs, vocab, seed):
 
 
 def run_designs(args):
-    """--designs [safupel|girolorn|zezilix]: a layer-list design next to a Llama (or the closest other design) of equal size (random weights): one prefill step of 4 x 2048 tokens,
+    """--designs [safupel|girolorn|zezilix|balenex]: a layer-list design next to a Llama (or the closest other design) of equal size (random weights): one prefill step of 4 x 2048 tokens,
     one decode step of 64 requests at context 2048, wall-clock per step plus per-kernel device times against the roofline."""
     from kge_loader import load
     kge = load()
@@ -637,6 +661,7 @@ def run_designs(args):
     B, ctx, PB, bs = 64, 2048, 4, args.block_size
     which = args.designs
     sizes, make, arms = {"girolorn": (GIROLORN_SIZES, girolorn_configs, ("girolorn", "llama")), "zezilix": (ZEZILIX_SIZES, zezilix_configs, ("zezilix", "girolorn")),
+                         "balenex": (BALENEX_SIZES, balenex_configs, ("balenex", "safupel")),
                          "safupel": (DESIGN_SIZES, design_configs, ("safupel", "llama"))}[which]
     if args.sizes:
         sizes = {k: v for k, v in sizes.items() if k in args.sizes.split(",")}
@@ -704,7 +729,7 @@ def main():
     ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"], help="TP data path: peer memory (default) or NCCL")
     ap.add_argument("--tp-timeout", type=float, default=420.0, help="seconds the tensor-parallel leg may take at N > 1")
     ap.add_argument("--sizes", default="", help="with --designs: the sizes to run, with commas between them (all by default)")
-    ap.add_argument("--designs", nargs="?", const="safupel", default=None, choices=["safupel", "girolorn", "zezilix"],
+    ap.add_argument("--designs", nargs="?", const="safupel", default=None, choices=["safupel", "girolorn", "zezilix", "balenex"],
                     help="instead of the workload: a layer-list design (safupel, the default, or girolorn) beside a Llama of equal "
                     "size, prefill and decode steps with per-kernel rooflines (one GPU, random weights)")
     args = ap.parse_args()

@@ -441,35 +441,43 @@ int kv_write_any(const void* k, int ldk, const void* v, int ldv, const int64_t* 
   return 0;
 }
 
-// One block per token; only a token that ends a block of `pool` positions has work: the block's keys and values are read
-// back from the caches (so what is averaged is what the attention reads), summed in fp32 in ascending position and
-// divided by the count.
+// One block per (token, key/value head); only a token that ends a block of `pool` positions has work: the block's keys
+// and values are read back from the caches (so what is averaged is what the attention reads), sixteen rows requested at a
+// time, summed in fp32 in ascending position and divided by the count.  One column per thread and pass.
 template <typename E>
-__global__ void __launch_bounds__(128) pool_kv_write_kernel(PoolKvArgs a) {
+__global__ void __launch_bounds__(256) pool_kv_write_kernel(PoolKvArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x, pos = a.positions[t];
+  const int t = blockIdx.x, g = blockIdx.y, pos = a.positions[t];
   if ((pos + 1) % a.pool != 0) return;
   const int pb = pos / a.pool, p0 = pb * a.pool;
   const int32_t* bt = a.block_table + (int64_t)a.token_req[t] * a.max_blocks;
-  const int64_t dblk = bt[pb / a.pool_slots], doff = pb % a.pool_slots;
-  const int nk = a.G * a.dim, nv = a.G * a.vdim;
-  for (int c = threadIdx.x; c < nk + nv; c += blockDim.x) {
-    const bool isk = c < nk;
-    const int cc = isk ? c : c - nk, w = isk ? a.dim : a.vdim, g = cc / w, dd = cc % w;
+  const int64_t drow = ((int64_t)bt[pb / a.pool_slots] * a.G + g) * a.pool_slots + pb % a.pool_slots;
+  for (int c = threadIdx.x; c < a.dim + a.vdim; c += blockDim.x) {
+    const bool isk = c < a.dim;
+    const int w = isk ? a.dim : a.vdim, dd = isk ? c : c - a.dim;
     const E* src = (const E*)(isk ? a.k_cache : a.v_cache);
     float acc = 0.f;
-    for (int j = p0; j <= pos; ++j) acc += ldf(src + (((int64_t)bt[j / a.block_size] * a.G + g) * a.block_size + j % a.block_size) * w + dd);
+    for (int j0 = p0; j0 <= pos; j0 += 16) {
+      float v[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const int j = j0 + u;
+        v[u] = j <= pos ? ldf(src + (((int64_t)bt[j / a.block_size] * a.G + g) * a.block_size + j % a.block_size) * w + dd) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 16; ++u) acc += v[u];
+    }
     E* dst = (E*)(isk ? a.pk_cache : a.pv_cache);
-    stf(dst + ((dblk * a.G + g) * a.pool_slots + doff) * w + dd, acc / (float)a.pool);
+    stf(dst + drow * w + dd, acc / (float)a.pool);
   }
 }
 
 int pool_kv_write(const PoolKvArgs& a, cudaStream_t st) {
   if (a.T <= 0) return 0;
-  KGE_REQUIRE(a.pool >= 1 && a.pool_slots >= 1 && a.pool_slots * a.pool >= a.block_size, "pool_kv_write: blocks of %d positions, %d entries per page of %d", a.pool, a.pool_slots, a.block_size);
-  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(pool_kv_write_kernel<float>, dim3(a.T), dim3(128), 0, st, a)
-                                        : launch_pdl(pool_kv_write_kernel<__nv_bfloat16>, dim3(a.T), dim3(128), 0, st, a);
+  KGE_REQUIRE(a.pool >= 1 && a.pool_slots >= 1 && a.pool_slots * a.pool >= a.block_size && a.G <= 65535, "pool_kv_write: blocks of %d positions, %d entries per page of %d", a.pool, a.pool_slots, a.block_size);
+  cudaError_t ce = a.elt == KGE_ELT_F32 ? launch_pdl(pool_kv_write_kernel<float>, dim3(a.T, a.G), dim3(256), 0, st, a)
+                                        : launch_pdl(pool_kv_write_kernel<__nv_bfloat16>, dim3(a.T, a.G), dim3(256), 0, st, a);
   KGE_CUDA_OK(ce);
   return 0;
 }

@@ -31,6 +31,8 @@ bool paged_attn_extras_decode_ok(int B, int H, int KV, int hd, int block_size);
 // gemm_tc.cu: one tcgen05 launch over row groups padded to 256 (the experts of a prompt step)
 int gemm_grouped(void* y, const void* x, const void* w, int T, int N, int K, int groups, const int32_t* tile_group, int glu, float glu_alpha,
                  float glu_limit, cudaStream_t st);
+// gemm_tc.cu: silu(x w[:f]^T + b[:f]) * (x w[f:]^T + b[f:]) with the pair formed in the epilogue; f a multiple of 64, K of 8
+int gemm_silu_gate_bias(void* y, const void* x, const void* w_gate_up, const void* bias_gate_up, int T, int f, int K, cudaStream_t st);
 }
 
 namespace {
@@ -891,8 +893,14 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       // silu(gate h + b) * (up h + b): one product over [gate | up] with the biases, the pair formed from its rows
       const int f = h.ff;
       void* act = at(e->ffbuf, (int64_t)2 * f * T);
-      DENSE(e->ffbuf, 2 * f, e->hx, d, L.up, T, ACT_NONE);
-      HFWD(C_ACT, (double)T * f * 3 * es, 0, silu_mul_halves(act, e->ffbuf, T, f, elt, st));
+      if (!e->f32 && f % 64 == 0 && d % 8 == 0) {
+        // [T, 2f] never reaches memory: biases and the gated pair in the epilogue of the tensor-core GEMM
+        HFWD(T <= 256 ? C_GEMM_S : C_GEMM_L, es * (2.0 * f * d + (double)T * (d + f)), 4.0 * T * (double)f * d,
+             gemm_silu_gate_bias(act, e->hx, L.ff_gate, L.ff_gate_b, T, f, d, st));
+      } else {
+        DENSE(e->ffbuf, 2 * f, e->hx, d, L.up, T, ACT_NONE);
+        HFWD(C_ACT, (double)T * f * 3 * es, 0, silu_mul_halves(act, e->ffbuf, T, f, elt, st));
+      }
       DENSE(e->obuf2, d, act, f, L.down, T, ACT_NONE);
       add_src(e->obuf2, d, 1.f);
     } else if (h.mlp == HybridLayerSpec::DENSE && h.ff_limit > 0.f) {

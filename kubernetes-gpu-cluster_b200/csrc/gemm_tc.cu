@@ -168,7 +168,9 @@ __host__ __device__ constexpr int xbuf_bytes(int tokn) { return (tokn + 8) * BLK
 // GATED: the 128 MMA rows of a tile are 64 gate rows (TMEM lanes 0-63) and the matching 64 up rows
 // (lanes 64-127) of a stacked [2f, K] weight; the epilogue emits silu(gate) * up for the 64
 // outputs with vLLM's cast points (vllm:model_executor/layers/activation.py:137-141).
-__device__ __forceinline__ float silu_gate_bf16(const GemmParams& p, float g_acc, float u_acc) {
+// n: the output column; with a bias ([gate | up] halves of p.N numbers each) it joins the accumulators before the rounding.
+__device__ __forceinline__ float silu_gate_bf16(const GemmParams& p, float g_acc, float u_acc, int n) {
+  if (p.bias && n < p.N) { g_acc += bf2f(p.bias[n]); u_acc += bf2f(p.bias[p.N + n]); }
   float g = rbf(g_acc), u = rbf(u_acc);                  // the gate_up GEMM output is bf16
   if (p.glu == 1) {                                      // clamped pair with a sigmoid gate: fp32 from the rounded pre-activations
     g = fminf(g, p.glu_limit);
@@ -506,7 +508,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 float o[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                  if (GATED) o[k] = silu_gate_bf16(p, a[ci][k], u[ci][k]);
+                  if (GATED) o[k] = silu_gate_bf16(p, a[ci][k], u[ci][k], n0 + k);
                   else { o[k] = a[ci][k] + bv4[k]; o[k] = apply_act(o[k], p.act); }
                 }
                 bf16* dst = p.y + (int64_t)t * p.N + n0;
@@ -570,7 +572,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
               const int t = t0 + c + col;
               const float gacc = is_up ? hb[(8 + j) * 64 + r64] : __uint_as_float(r[j]);
               const float uacc = is_up ? __uint_as_float(r[8 + j]) : hb[j * 64 + r64];
-              if (t < p.T) p.y[(int64_t)t * p.N + n] = f2bf(silu_gate_bf16(p, gacc, uacc));
+              if (t < p.T) p.y[(int64_t)t * p.N + n] = f2bf(silu_gate_bf16(p, gacc, uacc, n));
             }
           }
         }
@@ -629,7 +631,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             if (GATED) {
-              a[k] = silu_gate_bf16(p, a[k], u[k]);
+              a[k] = silu_gate_bf16(p, a[k], u[k], n0 + k);
             } else {
               if (p.bias && n0 + k < p.N) a[k] += bf2f(p.bias[n0 + k]);
               a[k] = apply_act(a[k], p.act);
@@ -811,7 +813,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         if (GATED) {
-          o[j] = silu_gate_bf16(p, a[j], up[j]);
+          o[j] = silu_gate_bf16(p, a[j], up[j], n0 + u * UNIT + j);
         } else {
           const int n = n0 + u * UNIT + j;
           float v = a[j] + ((p.bias && n < p.N) ? bf2f(p.bias[n]) : 0.f);
@@ -1317,7 +1319,7 @@ extern "C" int KGE_GEMM_NAME(void* y, const void* x, const void* w, const void* 
 }
 
 static int gemm_gated(void* y, const void* x, const void* w_gate_up, int T, int f, int K, int glu, float glu_alpha, float glu_limit, void* workspace,
-                      int64_t workspace_bytes, void* stream) {
+                      int64_t workspace_bytes, void* stream, const void* bias_gate_up = nullptr) {
   KGE_REQUIRE(y && x && w_gate_up, "kge_gemm_silu_gate_bf16: null pointer");
   KGE_REQUIRE(T >= 0 && f > 0 && K > 0 && K % 8 == 0, "kge_gemm_silu_gate_bf16: K=%d must be a positive multiple of 8", K);
   KGE_REQUIRE(f % 64 == 0, "kge_gemm_silu_gate_bf16: f=%d must be a multiple of 64", f);
@@ -1332,7 +1334,7 @@ static int gemm_gated(void* y, const void* x, const void* w_gate_up, int T, int 
     GemmPlan gw;
     if (plan_wide(T, f, K, true, gw)) {
       GemmParams p;
-      p.y = (bf16*)y; p.bias = nullptr; p.T = T; p.N = f; p.K = K; p.act = 2; p.glu = glu; p.glu_alpha = glu_alpha; p.glu_limit = glu_limit;
+      p.y = (bf16*)y; p.bias = (const bf16*)bias_gate_up; p.T = T; p.N = f; p.K = K; p.act = 2; p.glu = glu; p.glu_alpha = glu_alpha; p.glu_limit = glu_limit;
       p.l2_hints = 0; p.trace = g_gemm_trace; p.ws_count = nullptr; p.ws_part = nullptr;
       p.m_tiles = gw.m_tiles; p.n_tiles = 1; p.splits = gw.splits; p.kb_total = gw.kb_total; p.kb_per_split = gw.kb_per_split;
       CUtensorMap tw, tx;
@@ -1345,7 +1347,7 @@ static int gemm_gated(void* y, const void* x, const void* w_gate_up, int T, int 
   GemmPlan g = plan_gemm(T, f, K, 64, workspace != nullptr);
   if (g.ws && (workspace_bytes < ws_bytes_of(g) || ((uintptr_t)workspace & 15) != 0)) g = plan_gemm(T, f, K, 64);
   GemmParams p;
-  p.y = (bf16*)y; p.bias = nullptr; p.T = T; p.N = f; p.K = K; p.act = 2; p.glu = glu; p.glu_alpha = glu_alpha; p.glu_limit = glu_limit;
+  p.y = (bf16*)y; p.bias = (const bf16*)bias_gate_up; p.T = T; p.N = f; p.K = K; p.act = 2; p.glu = glu; p.glu_alpha = glu_alpha; p.glu_limit = glu_limit;
   p.l2_hints = tunable(TUN_GEMM_L2_HINTS);
   p.trace = g_gemm_trace;
   p.ws_count = g.ws ? (unsigned int*)workspace : nullptr;
@@ -1370,6 +1372,10 @@ extern "C" int KGE_GEMM_GLU_NAME(void* y, const void* x, const void* w_gate_up, 
 
 namespace kge {
 inline namespace KGE_ELT_NS {
+// the gated front half with biases: y[T, f] = silu(x w[:f]^T + b[:f]) * (x w[f:]^T + b[f:]), w [2f, K] and b [2f] stacked [gate | up]
+int gemm_silu_gate_bias(void* y, const void* x, const void* w_gate_up, const void* bias_gate_up, int T, int f, int K, cudaStream_t st) {
+  return gemm_gated(y, x, w_gate_up, T, f, K, 0, 0.f, 0.f, nullptr, 0, st, bias_gate_up);
+}
 // Grouped rows (the experts of a mixture, prompt steps): x [T, K] holds every group's rows padded to a multiple of 256,
 // w stacks `groups` weight matrices ([N, K] each, or [2f, K] = [gate | up] with glu >= 0), tile_group (device, T / 256
 // entries) names the matrix of every 256 rows.  y [T, N] (or [T, f]).  One launch for all groups, T > 256.

@@ -42,12 +42,15 @@ __global__ void __launch_bounds__(GN_THREADS) group_rmsnorm_kernel(E* y, const f
   for (int c = threadIdx.x; c < d; c += GN_THREADS) stf(y + (int64_t)r * d + c, row[c] * inv[c / gs] * ldf(w + c) * out_scale);
 }
 
-template <typename E>
+// VEC: four neighbouring columns per thread and pass (rows and groups of 4-column multiples, 16-byte aligned): 8-byte
+// loads of 16-bit rows, 16-byte ones of fp32 rows; the sums are formed in the same order either way
+template <typename E, bool VEC>
 __global__ void __launch_bounds__(GN_THREADS) postnorm_residual_kernel(PostNormArgs a) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float gn_sm[];
   const int d = a.d, t = blockIdx.x, gs = d / a.groups;
+  constexpr int W = VEC ? 4 : 1;
   float* ya = gn_sm;                 // the sublayer's result, then the new residual row
   float* yb = gn_sm + d;             // the second source
   __shared__ float inv[GN_MAX_GROUPS], red[33];
@@ -56,29 +59,51 @@ __global__ void __launch_bounds__(GN_THREADS) postnorm_residual_kernel(PostNormA
     const E* s = (const E*)a.src[i] + (int64_t)t * a.ld[i];
     float* dst = i ? yb : ya;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < d; c += GN_THREADS) { const float v = ldf(s + c); dst[c] = v; ss = fmaf(v, v, ss); }
+    for (int c = threadIdx.x * W; c < d; c += GN_THREADS * W) {
+      float v[4];
+      if (VEC) ld4(s + c, v); else v[0] = ldf(s + c);
+#pragma unroll
+      for (int k = 0; k < W; ++k) { dst[c + k] = v[k]; ss = fmaf(v[k], v[k], ss); }
+    }
     if (a.inner_w[i]) f[i] = 1.f / sqrtf(block_sum(ss, red) / (float)d + a.eps);
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < d; c += GN_THREADS) {
-    float v = a.inner_w[0] ? ya[c] * f[0] * ldf((const E*)a.inner_w[0] + c) : ya[c];
-    if (a.nsrc > 1) v += a.inner_w[1] ? yb[c] * f[1] * ldf((const E*)a.inner_w[1] + c) : yb[c];
-    ya[c] = v * a.src_scale;
+  for (int c = threadIdx.x * W; c < d; c += GN_THREADS * W) {
+    float w0[4] = {1.f, 1.f, 1.f, 1.f}, w1[4] = {1.f, 1.f, 1.f, 1.f};
+    if (a.inner_w[0]) { if (VEC) ld4((const E*)a.inner_w[0] + c, w0); else w0[0] = ldf((const E*)a.inner_w[0] + c); }
+    if (a.nsrc > 1 && a.inner_w[1]) { if (VEC) ld4((const E*)a.inner_w[1] + c, w1); else w1[0] = ldf((const E*)a.inner_w[1] + c); }
+#pragma unroll
+    for (int k = 0; k < W; ++k) {
+      float v = a.inner_w[0] ? ya[c + k] * f[0] * w0[k] : ya[c + k];
+      if (a.nsrc > 1) v += a.inner_w[1] ? yb[c + k] * f[1] * w1[k] : yb[c + k];
+      ya[c + k] = v * a.src_scale;
+    }
   }
   __syncthreads();
   group_inv_rms(ya, d, a.groups, a.eps, inv);
   __syncthreads();
   float* res = a.res + (int64_t)t * d;
-  for (int c = threadIdx.x; c < d; c += GN_THREADS) {
-    const float v = res[c] + ya[c] * inv[c / gs] * ldf((const E*)a.post_w + c);
-    res[c] = v;
-    ya[c] = v;
+  for (int c = threadIdx.x * W; c < d; c += GN_THREADS * W) {
+    float r[4], w[4];
+    if (VEC) { ld4(res + c, r); ld4((const E*)a.post_w + c, w); } else { r[0] = res[c]; w[0] = ldf((const E*)a.post_w + c); }
+    const float gi = inv[c / gs];
+#pragma unroll
+    for (int k = 0; k < W; ++k) { r[k] += ya[c + k] * gi * w[k]; ya[c + k] = r[k]; }
+    if (VEC) st4(res + c, r); else res[c] = r[0];
   }
   if (!a.next_w) return;
   __syncthreads();
   group_inv_rms(ya, d, a.groups, a.eps, inv);
   __syncthreads();
-  for (int c = threadIdx.x; c < d; c += GN_THREADS) stf((E*)a.next_y + (int64_t)t * d + c, ya[c] * inv[c / gs] * ldf((const E*)a.next_w + c));
+  E* ny = (E*)a.next_y + (int64_t)t * d;
+  for (int c = threadIdx.x * W; c < d; c += GN_THREADS * W) {
+    float w[4], o[4];
+    if (VEC) ld4((const E*)a.next_w + c, w); else w[0] = ldf((const E*)a.next_w + c);
+    const float gi = inv[c / gs];
+#pragma unroll
+    for (int k = 0; k < W; ++k) o[k] = ya[c + k] * gi * w[k];
+    if (VEC) st4(ny + c, o); else stf(ny + c, o[0]);
+  }
 }
 
 template <typename E>
@@ -120,12 +145,19 @@ int postnorm_residual(const PostNormArgs& a, cudaStream_t st) {
   KGE_REQUIRE(a.groups >= 1 && a.groups <= GN_MAX_GROUPS && a.d % a.groups == 0 && a.d <= 25600 && a.nsrc >= 1 && a.nsrc <= 2 && a.post_w,
               "postnorm_residual: %d groups of a row of %d, %d sources", a.groups, a.d, a.nsrc);
   const size_t smem = (size_t)a.d * 8;
+  bool vec = a.d % 4 == 0 && (a.d / a.groups) % 4 == 0 && ((uintptr_t)a.res & 15) == 0 && ((uintptr_t)a.post_w & 15) == 0 &&
+             (!a.next_w || ((((uintptr_t)a.next_w | (uintptr_t)a.next_y) & 15) == 0));
+  for (int i = 0; i < a.nsrc; ++i) vec = vec && a.ld[i] % 4 == 0 && ((uintptr_t)a.src[i] & 15) == 0 && (!a.inner_w[i] || ((uintptr_t)a.inner_w[i] & 15) == 0);
   if (a.elt == KGE_ELT_F32) {
-    if (int rc = opt_in_smem(postnorm_residual_kernel<float>, smem)) return rc;
-    KGE_CUDA_OK(launch_pdl(postnorm_residual_kernel<float>, dim3(a.T), dim3(GN_THREADS), smem, st, a));
+    if (int rc = opt_in_smem(postnorm_residual_kernel<float, false>, smem)) return rc;
+    if (int rc = opt_in_smem(postnorm_residual_kernel<float, true>, smem)) return rc;
+    KGE_CUDA_OK(vec ? launch_pdl(postnorm_residual_kernel<float, true>, dim3(a.T), dim3(GN_THREADS), smem, st, a)
+                    : launch_pdl(postnorm_residual_kernel<float, false>, dim3(a.T), dim3(GN_THREADS), smem, st, a));
   } else {
-    if (int rc = opt_in_smem(postnorm_residual_kernel<__nv_bfloat16>, smem)) return rc;
-    KGE_CUDA_OK(launch_pdl(postnorm_residual_kernel<__nv_bfloat16>, dim3(a.T), dim3(GN_THREADS), smem, st, a));
+    if (int rc = opt_in_smem(postnorm_residual_kernel<__nv_bfloat16, false>, smem)) return rc;
+    if (int rc = opt_in_smem(postnorm_residual_kernel<__nv_bfloat16, true>, smem)) return rc;
+    KGE_CUDA_OK(vec ? launch_pdl(postnorm_residual_kernel<__nv_bfloat16, true>, dim3(a.T), dim3(GN_THREADS), smem, st, a)
+                    : launch_pdl(postnorm_residual_kernel<__nv_bfloat16, false>, dim3(a.T), dim3(GN_THREADS), smem, st, a));
   }
   return 0;
 }
