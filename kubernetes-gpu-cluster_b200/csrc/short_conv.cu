@@ -1,6 +1,8 @@
 // A short causal convolution over time on every channel of a projection, continued across steps from a state slot that
 // holds the request's last taps - 1 input rows.  Each output is a sum over the taps in ascending order in fp32, from
 // this step's rows or the slot's, so the result does not depend on where a prompt was cut.
+#include <algorithm>
+
 #include "common.cuh"
 #include "elt_access.cuh"
 #include "hybrid_ops.h"
@@ -11,28 +13,27 @@ namespace {
 
 constexpr int SC_MAX_TAPS = 16;
 
-// one thread per (token, channel): its taps' inputs and weights are requested together, then summed in ascending order
+// a block per token and slice of the channels (few tokens: one channel per thread; many: a thread walks its channels);
+// a channel's taps are summed in ascending order
 template <typename E>
 __global__ void __launch_bounds__(256) short_conv_kernel(ShortConvArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
-  if (c >= a.C) return;
+  const int t = blockIdx.x;
   const int b = a.token_req[t], r0 = a.qsl[b], pos = a.positions[t], taps = a.taps;
   const float* sp = a.state + (int64_t)a.slots[b] * a.slot_stride;      // [taps - 1, C]: row s holds the input of position p0 - (taps - 1) + s
   const E* x = (const E*)a.x;
-  float u[SC_MAX_TAPS], w[SC_MAX_TAPS];
-#pragma unroll
-  for (int j = 0; j < SC_MAX_TAPS; ++j) {
-    const int back = taps - 1 - j, row = t - back;    // the input of position pos - back
-    const bool on = j < taps && pos - back >= 0;
-    u[j] = !on ? 0.f : (row >= r0 ? ldf(x + (int64_t)row * a.ldx + c) : sp[(int64_t)(taps - 1 - (r0 - row)) * a.C + c]);
-    w[j] = on ? ldf((const E*)a.w + (int64_t)c * taps + j) : 0.f;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < a.C; c += gridDim.y * blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int back = taps - 1 - j;                  // the input of position pos - back
+      if (pos - back < 0) continue;
+      const int row = t - back;
+      const float u = row >= r0 ? ldf(x + (int64_t)row * a.ldx + c) : sp[(int64_t)(taps - 1 - (r0 - row)) * a.C + c];
+      acc = fmaf(ldf((const E*)a.w + (int64_t)c * taps + j), u, acc);
+    }
+    stf((E*)a.y + (int64_t)t * a.ldy + c, acc);
   }
-  float acc = 0.f;
-#pragma unroll
-  for (int j = 0; j < SC_MAX_TAPS; ++j) acc = fmaf(w[j], u[j], acc);      // taps that are off add an exact zero
-  stf((E*)a.y + (int64_t)t * a.ldy + c, acc);
 }
 
 // one block per request: the slot's rows move up by the step's row count and the step's last rows follow
@@ -66,11 +67,12 @@ int short_conv_state(const ShortConvArgs& a, cudaStream_t st) {
   KGE_REQUIRE(a.taps >= 1 && a.taps <= SC_MAX_TAPS && a.C > 0 && a.x != a.y, "short_conv_state: %d taps on %d channels", a.taps, a.C);
   const int cb = (a.C + 255) / 256;
   KGE_REQUIRE(cb <= 65535, "short_conv_state: %d channels", a.C);
+  const int cy = std::max(1, std::min(cb, 2048 / std::max(a.T, 1)));     // about 2048 blocks at least, else a block per token
   if (a.elt == KGE_ELT_F32) {
-    KGE_CUDA_OK(launch_pdl(short_conv_kernel<float>, dim3(a.T, cb), dim3(256), 0, st, a));
+    KGE_CUDA_OK(launch_pdl(short_conv_kernel<float>, dim3(a.T, cy), dim3(256), 0, st, a));
     KGE_CUDA_OK(launch_pdl(short_conv_save_kernel<float>, dim3(a.B, cb), dim3(256), 0, st, a));
   } else {
-    KGE_CUDA_OK(launch_pdl(short_conv_kernel<__nv_bfloat16>, dim3(a.T, cb), dim3(256), 0, st, a));
+    KGE_CUDA_OK(launch_pdl(short_conv_kernel<__nv_bfloat16>, dim3(a.T, cy), dim3(256), 0, st, a));
     KGE_CUDA_OK(launch_pdl(short_conv_save_kernel<__nv_bfloat16>, dim3(a.B, cb), dim3(256), 0, st, a));
   }
   return 0;
