@@ -129,13 +129,24 @@ __device__ __forceinline__ float capped_log2(float s, float cap_in2, float cap_l
   return fmaf(-2.f * cap_log2, rcp_ftz(e + 1.f), cap_log2);
 }
 
-template <int HD, bool TMA, bool CAP = false>
+// A sliding window with kept first tokens or pooled blocks (WIN kernels; TMA only).  A row at position i sees the keys
+// j in (i - window, i], and before them its prefix keys: the first min(keep_first, i - window + 1) positions (their own
+// cache rows), or the first (i - window + 1) / pool entries of the pooled caches (tm_pk / tm_pv: [blocks, KV, pool_slots, HD],
+// entry u of a request in its page u / pool_slots).  The CTA walks the prefix keys in tiles of their own, then the tiles
+// that hold its rows' windows.
+struct WinArgs {
+  int window = 0, keep_first = 0, pool = 0, pool_slots = 0;
+};
+
+template <int HD, bool TMA, bool CAP = false, bool WIN = false>
 __global__ void __launch_bounds__(TMA ? 192 : 160, 2)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                bf16* __restrict__ out, const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache,
                const bf16* __restrict__ v_cache, const int32_t* __restrict__ block_table, int max_blocks,
                const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ qsl, int H, int KV, int bs_shift,
-               float scale_log2_in, float cap_in2, float cap_log2, const float* __restrict__ sinks) {
+               float scale_log2_in, float cap_in2, float cap_log2, const float* __restrict__ sinks,
+               const __grid_constant__ CUtensorMap tm_pk, const __grid_constant__ CUtensorMap tm_pv, WinArgs win) {
+  static_assert(!WIN || TMA, "window kernels fetch their tiles by TMA");
   const float scale_log2 = CAP ? 1.f : scale_log2_in;    // capped scores are formed in units of log 2
   constexpr int CH = HD / 8;                       // 16-byte chunks per row
   constexpr uint32_t Q_BYTES = 128 * HD * 2;
@@ -158,7 +169,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
   const int ctx0 = seq_len - q_len;
   const int ntok = min(TT, q_len - tok0);
   const int kv_len = ctx0 + tok0 + ntok;
-  const int ntiles = (kv_len + BNK - 1) / BNK;
+  // WIN: ptiles tiles of prefix keys (the CTA's last row sees the most), then the tiles from the one that holds the first
+  // row's oldest window key to the diagonal
+  auto prefix_of = [&](int pos) {
+    const int before = pos - win.window + 1;          // positions 0 .. before - 1 have left the window
+    return before <= 0 ? 0 : (win.pool > 0 ? before / win.pool : min(win.keep_first, before));
+  };
+  const int pre_cta = WIN ? prefix_of(kv_len - 1) : 0, ptiles = (pre_cta + BNK - 1) / BNK;
+  const int tile_lo = WIN ? max(0, ctx0 + tok0 - win.window + 1) / BNK : 0;
+  const int ntiles = ptiles + (kv_len + BNK - 1) / BNK - tile_lo;
   const int32_t* btab = block_table + (int64_t)b * max_blocks;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -256,8 +275,22 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
         const uint32_t dst = (is_k ? sK : sV) + st * TILE_BYTES;
         const uint32_t bar = is_k ? k_full(st) : v_full(st);
         mbar_expect_tx(bar, TILE_BYTES);
+        if (WIN && t < ptiles && win.pool > 0) {
+          // a tile of pooled entries: boxes of min(pool_slots, 64) rows, each inside one page's entries
+          const int ps = win.pool_slots, prow = ps < BNK ? ps : BNK;
+          for (int i = 0; i < BNK / prow; ++i) {
+            const int u = t * BNK + i * prow, bi = u / ps;
+            const int blk = (u < pre_cta && bi < max_blocks) ? btab[bi] : 0;      // past the CTA's entries: block 0 (masked)
+            const int row = (blk * KV + kvh) * ps + u % ps;
+#pragma unroll
+            for (int h = 0; h < HD / 64; ++h)
+              tma_load_2d(dst + (uint32_t)(h * (BNK * 128) + i * prow * 128), is_k ? &tm_pk : &tm_pv, bar, h * 64, row);
+          }
+          return;
+        }
+        const int tkey = WIN ? (t < ptiles ? t : tile_lo + t - ptiles) : t;      // the tile of positions this stage holds
         for (int i = 0; i < boxes; ++i) {
-          const int key = t * BNK + i * box_rows;
+          const int key = tkey * BNK + i * box_rows;
           const int bi = key >> bs_shift;
           const int blk = bi < max_blocks ? btab[bi] : 0;      // past the table: block 0 (those keys are masked)
           const int row = (blk * KV + kvh) * bs + (key & (bs - 1));
@@ -283,6 +316,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
     const int tk = r / G, hh = r % G;
     const bool row_ok = tk < ntok;
     const int lim = row_ok ? ctx0 + tok0 + tk : -1;          // last visible key of this row
+    const int lo_row = (WIN && row_ok) ? max(0, lim - win.window + 1) : 0;      // first key of its window
+    const int npre = (WIN && row_ok) ? prefix_of(lim) : 0;                      // its prefix keys
     constexpr int RP = 128 / CH, NP = BNK / RP, NPQ = 128 / RP;
     const int lrow0 = tid / CH, lc = tid % CH;
     const int64_t head_off = ((int64_t)kvh << bs_shift) * HD;
@@ -341,7 +376,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
         load_tile(j + 2, true);
         if (j + 1 < ntiles) { cp_wait<2>(); fence_async_smem(); mbar_arrive(k_full((j + 1) & 1)); }
       }
-      const int kbase = j * BNK;
+      const bool ptile = WIN && j < ptiles;
+      const int kbase = WIN ? (ptile ? j * BNK : (tile_lo + j - ptiles) * BNK) : j * BNK;
       uint32_t sv[BNK];
 #pragma unroll
       for (int c = 0; c < BNK; c += 32) tmem_ld32(t_row + (j & 1) * BNK + c, *reinterpret_cast<uint32_t(*)[32]>(&sv[c]));
@@ -351,7 +387,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
       // four independent running maxima (and, below, sums): with two softmax warps per scheduler there is little
       // else to hide the latency of a 64-long dependent chain behind
       float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      if (__all_sync(0xffffffffu, kbase + BNK - 1 <= lim)) {
+      if (__all_sync(0xffffffffu, WIN ? (ptile ? kbase + BNK <= npre : (kbase + BNK - 1 <= lim && kbase >= lo_row)) : kbase + BNK - 1 <= lim)) {
 #pragma unroll
         for (int i = 0; i < BNK; ++i) {
           if (CAP) sv[i] = __float_as_uint(capped_log2(__uint_as_float(sv[i]), cap_in2, cap_log2));
@@ -361,7 +397,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
 #pragma unroll
         for (int i = 0; i < BNK; ++i) {
           const float raw = CAP ? capped_log2(__uint_as_float(sv[i]), cap_in2, cap_log2) : __uint_as_float(sv[i]);
-          const float x = (kbase + i <= lim) ? raw : -INFINITY;
+          const bool vis = WIN ? (ptile ? kbase + i < npre : (kbase + i <= lim && kbase + i >= lo_row)) : kbase + i <= lim;
+          const float x = vis ? raw : -INFINITY;
           sv[i] = __float_as_uint(x);
           mxa[i & 3] = fmaxf(mxa[i & 3], x);
         }
@@ -472,15 +509,62 @@ static int launch_tc(bf16* out, const bf16* q, int q_stride, const bf16* kc, con
     auto kern = cap ? atc::attn_tc_kernel<HD, true, true> : atc::attn_tc_kernel<HD, true, false>;
     KGE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, atc::tc_smem<HD>()));
     KGE_CUDA_OK(launch_pdl(kern, dim3((max_q_len + TT - 1) / TT, KV, B), dim3(192), atc::tc_smem<HD>(), st, tk, tv, out, q, q_stride,
-                           kc, vc, bt, max_blocks, sl, qsl, H, KV, bs_shift, scale * atc::kLog2e, cap_in2, cap_log2, sinks));
+                           kc, vc, bt, max_blocks, sl, qsl, H, KV, bs_shift, scale * atc::kLog2e, cap_in2, cap_log2, sinks, tk, tv, atc::WinArgs()));
     return 0;
   }
   memset(&tk, 0, sizeof tk); memset(&tv, 0, sizeof tv);
   auto kern = cap ? atc::attn_tc_kernel<HD, false, true> : atc::attn_tc_kernel<HD, false, false>;
   KGE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, atc::tc_smem<HD>()));
   KGE_CUDA_OK(launch_pdl(kern, dim3((max_q_len + TT - 1) / TT, KV, B), dim3(160), atc::tc_smem<HD>(), st, tk, tv, out, q, q_stride, kc,
-                         vc, bt, max_blocks, sl, qsl, H, KV, bs_shift, scale * atc::kLog2e, cap_in2, cap_log2, sinks));
+                         vc, bt, max_blocks, sl, qsl, H, KV, bs_shift, scale * atc::kLog2e, cap_in2, cap_log2, sinks, tk, tv, atc::WinArgs()));
   return 0;
+}
+
+template <int HD>
+static int launch_tc_window(bf16* out, const bf16* q, int q_stride, const bf16* kc, const bf16* vc, const bf16* pkc, const bf16* pvc, const int32_t* bt,
+                            int max_blocks, const int32_t* sl, const int32_t* qsl, int B, int max_q_len, int H, int KV, int bs, float scale,
+                            const atc::WinArgs& win, cudaStream_t st) {
+  int bs_shift = 0;
+  while ((1 << bs_shift) < bs) ++bs_shift;
+  const int TT = atc::BM / (H / KV);
+  CUtensorMap tk, tv, tpk, tpv;
+  const int box_rows = bs < atc::BNK ? bs : atc::BNK;
+  const int64_t rows = (int64_t)1 << 30;
+  if (int rc = make_tmap(&tk, kc, rows, HD, box_rows)) return rc;
+  if (int rc = make_tmap(&tv, vc, rows, HD, box_rows)) return rc;
+  tpk = tk; tpv = tv;
+  if (win.pool > 0) {
+    const int prow = win.pool_slots < atc::BNK ? win.pool_slots : atc::BNK;
+    if (int rc = make_tmap(&tpk, pkc, rows, HD, prow)) return rc;
+    if (int rc = make_tmap(&tpv, pvc, rows, HD, prow)) return rc;
+  }
+  auto kern = atc::attn_tc_kernel<HD, true, false, true>;
+  KGE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, atc::tc_smem<HD>()));
+  KGE_CUDA_OK(launch_pdl(kern, dim3((max_q_len + TT - 1) / TT, KV, B), dim3(192), atc::tc_smem<HD>(), st, tk, tv, out, q, q_stride, kc, vc, bt,
+                         max_blocks, sl, qsl, H, KV, bs_shift, scale * atc::kLog2e, 0.f, 0.f, (const float*)nullptr, tpk, tpv, win));
+  return 0;
+}
+
+// whether paged_attn_window_tc takes these sizes: 64- or 128-wide keys and values, pages of a power of two of at least 8
+// tokens, pooled entries per page that tile a 64-entry box (a power of two up to 64, or a multiple of 64)
+bool paged_attn_window_tc_ok(int H, int KV, int hd, int vd, int bs, int pool, int pool_slots) {
+  if (!(hd == 64 || hd == 128) || vd != hd || KV <= 0 || H % KV || H / KV > 128 || bs < 8 || (bs & (bs - 1)) || tunable(TUN_ATTN_TMA) == 0) return false;
+  if (pool > 0 && !((pool_slots <= 64 && (pool_slots & (pool_slots - 1)) == 0 && pool_slots > 0) || pool_slots % 64 == 0)) return false;
+  return true;
+}
+
+// Steps with prompt pieces, a sliding window with kept first tokens (keep_first > 0) or pooled blocks (pool > 0): the
+// tcgen05 kernel above with the window's tile range and masks.  Sizes: paged_attn_window_tc_ok.
+int paged_attn_window_tc(void* out, const void* q, int q_stride, const void* kc, const void* vc, const void* pkc, const void* pvc, const int32_t* bt,
+                         int max_blocks, const int32_t* sl, const int32_t* qsl, int B, int max_q_len, int H, int KV, int hd, int bs, float scale,
+                         int window, int keep_first, int pool, int pool_slots, cudaStream_t st) {
+  KGE_REQUIRE(window > 0 && paged_attn_window_tc_ok(H, KV, hd, hd, bs, pool, pool_slots), "paged_attn_window_tc: unsupported sizes");
+  atc::WinArgs win;
+  win.window = window; win.keep_first = keep_first; win.pool = pool; win.pool_slots = pool_slots;
+  if (hd == 128) return launch_tc_window<128>((bf16*)out, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, (const bf16*)pkc, (const bf16*)pvc, bt, max_blocks, sl, qsl, B,
+                                               max_q_len, H, KV, bs, scale, win, st);
+  return launch_tc_window<64>((bf16*)out, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, (const bf16*)pkc, (const bf16*)pvc, bt, max_blocks, sl, qsl, B, max_q_len,
+                              H, KV, bs, scale, win, st);
 }
 
 // Called by kge_paged_attn (attn.cu) for batches with query chunks longer than one token.

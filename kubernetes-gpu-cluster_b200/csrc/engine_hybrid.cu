@@ -28,6 +28,11 @@ int paged_attn_extras(void* out, const void* q, int q_stride, const void* k_cach
                       int max_seq_len, int H, int KV, int hd, int block_size, float scale, float softcap, const float* sinks, void* workspace,
                       int64_t workspace_bytes, void* stream);
 bool paged_attn_extras_decode_ok(int B, int H, int KV, int hd, int block_size);
+// attn_tc.cu: the tcgen05 prompt kernel with a sliding window and kept first tokens or pooled blocks (64- / 128-wide heads)
+bool paged_attn_window_tc_ok(int H, int KV, int hd, int vd, int bs, int pool, int pool_slots);
+int paged_attn_window_tc(void* out, const void* q, int q_stride, const void* kc, const void* vc, const void* pkc, const void* pvc, const int32_t* bt,
+                         int max_blocks, const int32_t* sl, const int32_t* qsl, int B, int max_q_len, int H, int KV, int hd, int bs, float scale,
+                         int window, int keep_first, int pool, int pool_slots, cudaStream_t st);
 // gemm_tc.cu: one tcgen05 launch over row groups padded to 256 (the experts of a prompt step)
 int gemm_grouped(void* y, const void* x, const void* w, int T, int N, int K, int groups, const int32_t* tile_group, int glu, float glu_alpha,
                  float glu_limit, cudaStream_t st);
@@ -755,8 +760,15 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
         const int before = std::max(hm.pos[t] - h.window + 1, 0);
         keys += std::min(hm.pos[t] + 1, h.window) + (h.pool > 0 ? before / h.pool : std::min(before, h.keep_first));
       }
+      // steps with prompt pieces, 64- / 128-wide heads, bfloat16: the tcgen05 kernel (TMA-staged tiles, S and O in TMEM) with the
+      // window's tile range; decode steps and everything else: the mma.sync / per-row kernels
+      const bool tc = !e->f32 && !decode_only && ldq % 8 == 0 && ((uintptr_t)qkv & 15) == 0 &&
+                      paged_attn_window_tc_ok(h.heads, h.kv_heads, h.dim, h.vdim, bs, h.pool, ps);
       HFWD(decode_only ? C_ATT_DEC : C_ATT_GEN, (decode_only ? keys : (double)T) * h.kv_heads * (h.dim + h.vdim) * es + (double)T * h.heads * (h.dim + h.vdim) * es,
-           2.0 * keys * h.heads * (h.dim + h.vdim), attn_bias_chunk(aa, st));
+           2.0 * keys * h.heads * (h.dim + h.vdim),
+           tc ? paged_attn_window_tc(e->mixbuf, qkv, ldq, L.kc, L.vc, L.pkc, L.pvc, m.btab, max_blocks, m.seq_lens, m.qsl, B, aa.max_q, h.heads, h.kv_heads, h.dim, bs,
+                                     h.scale, h.window, h.keep_first, h.pool, ps, st)
+              : attn_bias_chunk(aa, st));
       if (h.v_rot) HFWD(C_ACT, (double)T * ka * 2 * es, 0, rotate_heads_halves(e->mixbuf, ka, m.pos, L.v_freq, T, h.heads, h.vdim, -1.f, elt, st));
       DENSE(e->obuf1, d, e->mixbuf, ka, L.o, T, ACT_NONE);
       if (gla) {

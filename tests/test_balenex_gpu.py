@@ -357,6 +357,47 @@ def test_tensor_core_sizes(kge, tmp_path):
     check(lg[1:], ob.forward(cfg, W, c).numpy()[:66], "bfloat16", "a prompt piece beside a single token", noise)
 
 
+TC_HEADS = [("window", 4, 2, 64, 70, 3), ("window", 6, 2, 128, 100, 70), ("window", 2, 2, 64, 33, 0), ("pooled", 4, 1, 64, 70, 8), ("pooled", 8, 2, 128, 45, 64),
+            ("pooled", 2, 2, 64, 64, 2), ("pooled", 2, 1, 64, 40, 1), ("pooled", 4, 2, 64, 50, 5)]
+
+
+@pytest.mark.parametrize("shape", TC_HEADS)
+def test_tensor_core_head_sizes(kge, tmp_path, shape):
+    """bfloat16, 64-token pages, one attention mechanism alone with keys and values of 64 or 128 numbers: the sizes the
+    tcgen05 prompt kernel takes (prefix keys in tiles of their own - more kept tokens than a tile holds, pooled entries of 8, 1,
+    32 and 64 per page, and 13 per page, which the mma.sync kernel takes instead - then the window's tiles).  Prompt steps,
+    pieces, decoding over a page border, single tokens beside a prompt piece."""
+    kind, heads, kv, dim, size, extra = shape
+    if kind == "window":
+        L = ob.parallel_layer(heads=heads, kv_heads=kv, dim=dim, vdim=dim, size=size, keep_first=extra, rot_dims=dim // 2, base=1000.0, scale=6.0 / dim, conv=3, ff=0)
+    else:
+        L = ob.attention_layer(heads=heads, kv_heads=kv, dim=dim, vdim=dim, size=size, pool=extra, scale=6.0 / dim, ff=0)
+    cfg = ob.make_config([L, copy.deepcopy(L)], width=64, groups=2)
+    W = ob.make_weights(cfg, seed=23)
+    if kind == "window":
+        silence(W, "right.o")
+    toks = prompt(cfg, 330, 34)
+    want = ob.forward(cfg, W, toks)
+    noise = ob.bfloat16_noise(cfg, W, toks)
+    llm = make_engine(kge, tmp_path, cfg, W, "bfloat16", bs=64, tokens=1024)
+    check(run_pieces(llm, 0, toks, [330]), want, "bfloat16", "whole", noise)
+    llm.trace_end(0)
+    got = np.concatenate([run_pieces(llm, 1, toks[:280], [61, 3, 2, 64, 50, 100]), run_pieces(llm, 1, toks[280:], [1] * 50)])
+    check(got, want, "bfloat16", "pieces, then decoding", noise)
+    llm.trace_end(1)
+    a, c = prompt(cfg, 150, 35), prompt(cfg, 200, 37)
+    wa, wc = ob.forward(cfg, W, a).numpy(), ob.forward(cfg, W, c).numpy()
+    llm.trace_add(2, a[:140])
+    llm.trace_add(3, c[:131])
+    llm.trace_step([(2, 140, []), (3, 131, [])])
+    llm.trace_add(2, a[140:141])
+    llm.trace_add(3, c[131:])
+    lg = llm.trace_step([(2, 1, [0]), (3, 69, list(range(69)))])
+    llm.close()
+    check(lg[:1], wa[140:141], "bfloat16", "a single token beside a prompt piece", noise)
+    check(lg[1:], wc[131:], "bfloat16", "a prompt piece that starts inside a page beside a single token", noise)
+
+
 def test_first_tokens(kge, tmp_path):
     cfg = full()
     W = ob.make_weights(cfg, seed=11)
