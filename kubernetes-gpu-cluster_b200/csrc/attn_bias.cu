@@ -209,12 +209,13 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
     if (ptile) { if (jl < pre_cta) myrow = prefix_row(a, bt, g, jl); }
     else if (jl <= pos_last) myrow = ((int64_t)bt[jl / a.block_size] * a.G + g) * a.block_size + jl % a.block_size;
     const int sid = ROWS ? threadIdx.x : lane, sstep = ROWS ? AM_WARPS * 32 : 32;
-    // four 16-byte pieces are requested before the first is stored, so a tile costs a few memory round trips, not one
-    // per piece (whole warps run the loops: the shuffle needs every lane)
-    for (int idx0 = 0; idx0 < AM_KT * kseg; idx0 += 4 * sstep) {
-      uint4 v[4]; int dst[4];
+    // four 16-byte pieces (eight where one warp stages a whole tile: decoding) are requested before the first is stored, so
+    // a tile costs a few memory round trips, not one per piece (whole warps run the loops: the shuffle needs every lane)
+    constexpr int SU = ROWS ? 4 : 8;
+    for (int idx0 = 0; idx0 < AM_KT * kseg; idx0 += SU * sstep) {
+      uint4 v[SU]; int dst[SU];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < SU; ++u) {
         const int idx = min(idx0 + u * sstep + sid, AM_KT * kseg - 1);
         const int key = idx / kseg, seg = idx % kseg;
         const int64_t row = __shfl_sync(0xffffffffu, myrow, key);
@@ -223,12 +224,12 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
         dst[u] = key * kst + seg * 8;
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) *reinterpret_cast<uint4*>(Ks + dst[u]) = v[u];
+      for (int u = 0; u < SU; ++u) *reinterpret_cast<uint4*>(Ks + dst[u]) = v[u];
     }
-    for (int idx0 = 0; idx0 < AM_KT * vseg; idx0 += 4 * sstep) {
-      uint4 v[4]; int dst[4];
+    for (int idx0 = 0; idx0 < AM_KT * vseg; idx0 += SU * sstep) {
+      uint4 v[SU]; int dst[SU];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < SU; ++u) {
         const int idx = min(idx0 + u * sstep + sid, AM_KT * vseg - 1);
         const int key = idx / vseg, seg = idx % vseg;
         const int64_t row = __shfl_sync(0xffffffffu, myrow, key);
@@ -237,7 +238,7 @@ __global__ void __launch_bounds__(AM_WARPS * 32) attn_bias_mma_kernel(AttnBiasAr
         dst[u] = key * vst + seg * 8;
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) *reinterpret_cast<uint4*>(Vs + dst[u]) = v[u];
+      for (int u = 0; u < SU; ++u) *reinterpret_cast<uint4*>(Vs + dst[u]) = v[u];
     }
     if (ROWS) __syncthreads(); else __syncwarp();
     if (ROWS && (ptile ? j0 >= own_pre : (j0 > own_hi || j0 + AM_KT <= own_lo))) continue;

@@ -331,6 +331,33 @@ __global__ void __launch_bounds__(256) wkv_norm_gate_kernel(WkvArgs a) {
   }
 }
 
+// the same with four columns per lane and pass (head sizes and row strides of 4-column multiples, 16-byte aligned rows)
+template <typename E>
+__global__ void __launch_bounds__(256) wkv_norm_gate_vec_kernel(WkvArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (item >= (int64_t)a.T * a.H) return;
+  const int lane = threadIdx.x & 31, t = (int)(item / a.H), h = (int)(item % a.H), dim = a.vdim > 0 ? a.vdim : a.dim, HD = a.H * dim;
+  const float* o = a.o32 + (int64_t)t * HD + h * dim;
+  float ss = 0.f;
+  for (int c = lane * 4; c < dim; c += 128) {
+    float v[4];
+    ld4(o + c, v);
+    ss = fmaf(v[0], v[0], ss); ss = fmaf(v[1], v[1], ss); ss = fmaf(v[2], v[2], ss); ss = fmaf(v[3], v[3], ss);
+  }
+  const float inv = 1.f / sqrtf(warp_sum(ss) / (float)dim + a.eps);
+  const E* g = (const E*)a.gate_pre + (int64_t)t * a.ld + h * dim;
+  E* y = (E*)a.out + (int64_t)t * a.ldo + h * dim;
+  for (int c = lane * 4; c < dim; c += 128) {
+    float v[4], gv[4], w[4], r[4];
+    ld4(o + c, v); ld4(g + c, gv); ld4((const E*)a.norm_w + h * dim + c, w);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) r[k] = v[k] * inv * w[k] * (gv[k] / (1.f + expf(-gv[k])));
+    st4(y + c, r);
+  }
+}
+
 template <typename E>
 static int wkv_scan_t(const WkvArgs& a, cudaStream_t st) {
   const dim3 grid(a.B, a.H);
@@ -351,7 +378,10 @@ static int wkv_scan_t(const WkvArgs& a, cudaStream_t st) {
   else ce = launch_pdl(wkv_scan_kernel<E, 256>, grid, dim3(256), 0, st, a);
   KGE_CUDA_OK(ce);
   const int64_t items = (int64_t)a.T * a.H;
-  KGE_CUDA_OK(launch_pdl(wkv_norm_gate_kernel<E>, dim3((unsigned)((items + 7) / 8)), dim3(256), 0, st, a));
+  const bool vec = vd % 4 == 0 && a.ld % 4 == 0 && a.ldo % 4 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(a.o32) | reinterpret_cast<uintptr_t>(a.gate_pre) | reinterpret_cast<uintptr_t>(a.out) | reinterpret_cast<uintptr_t>(a.norm_w)) & 15) == 0;
+  if (vec) KGE_CUDA_OK(launch_pdl(wkv_norm_gate_vec_kernel<E>, dim3((unsigned)((items + 7) / 8)), dim3(256), 0, st, a));
+  else KGE_CUDA_OK(launch_pdl(wkv_norm_gate_kernel<E>, dim3((unsigned)((items + 7) / 8)), dim3(256), 0, st, a));
   return 0;
 }
 
