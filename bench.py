@@ -599,20 +599,20 @@ def zezilix_configs(z):
 
 BALENEX_SIZES = {
     # windowed attention beside gated linear attention, and windowed attention over pooled blocks (Balenex), at sizes that
-    # resemble real layers: 128-wide heads, a window of 1024 positions with 4 kept tokens or pooled blocks of 64, linear
+    # resemble real layers: 128-wide heads, a window of 1024 positions with 8 kept tokens or pooled blocks of 64, linear
     # attention with 64 x 64 states, a gated feed-forward; the model beside it is the closest one the engine has, the design
     # with attention and a matrix memory side by side and convolved recurrences (Safupel) of the same width, depth and heads
-    "w2048": dict(width=2048, vocab=32000, reps=2, heads=16, kv=4, dim=128, window=1024, keep=4, pool=64, rot=64, conv=4, r_heads=32, r_dim=64, r_vdim=64,
+    "w2048": dict(width=2048, vocab=32000, reps=2, heads=16, kv=4, dim=128, window=1024, keep=8, pool=64, rot=64, conv=4, r_heads=32, r_dim=64, r_vdim=64,
                   decay_rank=64, ff=5632, groups=8, safupel="w2048"),
-    "w4096": dict(width=4096, vocab=32000, reps=1, heads=32, kv=8, dim=128, window=1024, keep=4, pool=64, rot=64, conv=4, r_heads=64, r_dim=64, r_vdim=64,
+    "w4096": dict(width=4096, vocab=32000, reps=1, heads=32, kv=8, dim=128, window=1024, keep=8, pool=64, rot=64, conv=4, r_heads=64, r_dim=64, r_vdim=64,
                   decay_rank=64, ff=11008, groups=8, safupel="w4096"),
 }
 
 
 def balenex_configs(z):
     left = {"conv": z["conv"], "dim": z["dim"], "heads": z["heads"], "kv_heads": z["kv"], "mask": {"keep_first": z["keep"], "size": z["window"]},
-            "rot": {"base": 10000.0, "dims": z["rot"]}, "scale": z["dim"] ** -0.5, "vdim": z["dim"]}
-    right = {"dim": z["r_dim"], "heads": z["r_heads"], "tau": 16.0, "vdim": z["r_vdim"], "decay_rank": z["decay_rank"]}
+            "rot": {"base": 1000000.0, "dims": z["rot"]}, "scale": z["dim"] ** -0.5, "vdim": z["dim"]}
+    right = {"dim": z["r_dim"], "heads": z["r_heads"], "tau": 8.0, "vdim": z["r_vdim"], "decay_rank": z["decay_rank"]}
     att = {"dim": z["dim"], "heads": z["heads"], "kv_heads": z["kv"], "mask": {"pool": z["pool"], "size": z["window"]}, "scale": z["dim"] ** -0.5, "vdim": z["dim"]}
     dense = {"ff": z["ff"], "kind": "dense"}
     four = [{"mixer": {"left": left, "right": right}, "mlp": dense, "type": "parallel"}, {"mixer": att, "mlp": dense, "type": "attention"},

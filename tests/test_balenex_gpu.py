@@ -508,3 +508,60 @@ def test_trace_runner_command_line(kge, tmp_path):
         for st, rr in rows.items():
             got = np.fromfile(os.path.join(out, f"{st}.f32"), dtype="<f4").reshape(len(rr), cfg["vocab"])
             check(got, np.stack([want[k][i] for k, i in rr]), dtype, f"step {st}")
+
+
+def test_server_command_line_and_sampling(kge, tmp_path):
+    """`vllm serve DIR` picks the design from config.json: greedy completions over HTTP (token-id prompts) equal the
+    in-process engine's, in bfloat16 and with --dtype float32; sampling with a temperature and a seed is reproducible and
+    stays inside the vocabulary."""
+    import json
+    import os
+    import socket
+    import subprocess
+    import time
+    import urllib.request
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    binary = os.path.join(root, "kubernetes-gpu-cluster_b200", "bin", "vllm")
+    assert os.path.exists(binary), "build the server: make -C kubernetes-gpu-cluster_b200"
+    cfg = full()
+    W = ob.make_weights(cfg, seed=19)
+    d = str(tmp_path / "m")
+    ob.save_model_dir(d, cfg, W)
+    prompts = [prompt(cfg, n, 100 + n) for n in (23, 4, 40)]
+    for dtype in ("bfloat16", "float32"):
+        llm = kge.LLM(d, dtype=dtype, max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32, num_gpu_blocks_override=16, enable_prefix_caching=False)
+        ref = [o.outputs[0].token_ids for o in llm.generate(prompts, kge.SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))]
+        warm = [o.outputs[0].token_ids for o in llm.generate(prompts[:1], kge.SamplingParams(max_tokens=8, temperature=0.8, top_k=20, seed=7, ignore_eos=True))]
+        again = [o.outputs[0].token_ids for o in llm.generate(prompts[:1], kge.SamplingParams(max_tokens=8, temperature=0.8, top_k=20, seed=7, ignore_eos=True))]
+        llm.close()
+        assert warm == again and all(0 <= t < cfg["vocab"] for t in warm[0])
+        s = socket.socket()
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+        s.close()
+        proc = subprocess.Popen([binary, "serve", d, "--host", "127.0.0.1", "--port", str(port), "--dtype", dtype, "--max-model-len", "128", "--max-num-seqs", "4",
+                                 "--max-num-batched-tokens", "32", "--num-gpu-blocks-override", "16", "--served-model-name", "z", "--trust-remote-code"],
+                                stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        try:
+            t0 = time.time()
+            while True:
+                try:
+                    with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=2) as r:
+                        if r.status == 200:
+                            break
+                except Exception:
+                    pass
+                assert proc.poll() is None, proc.stderr.read()[-2000:]
+                assert time.time() - t0 < 120, "server did not come up"
+                time.sleep(0.2)
+            req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/completions", headers={"Content-Type": "application/json"},
+                                         data=json.dumps({"model": "z", "prompt": prompts, "max_tokens": 8, "temperature": 0, "ignore_eos": True}).encode())
+            with urllib.request.urlopen(req, timeout=60) as r:
+                body = json.loads(r.read().decode())
+            assert [c["token_ids"] for c in body["choices"]] == ref, dtype
+        finally:
+            proc.terminate()
+            try:
+                proc.wait(timeout=20)
+            except subprocess.TimeoutExpired:
+                proc.kill()
