@@ -11,7 +11,7 @@ namespace kge {
 
 namespace {
 
-constexpr int GN_THREADS = 256, GN_MAX_GROUPS = 64;
+constexpr int GN_THREADS = 256, GN_MAX_GROUPS = 1024;
 
 // sum of squares of every group of a shared row: warp w takes groups w, w + nwarps, ..; the result is the factor
 // 1 / sqrt(mean + eps) per group in inv[]
