@@ -897,7 +897,7 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
     }
     if (s.hyb_prenorm_pair && h.mlp != HybridLayerSpec::NONE) {
       // the feed-forward reads a norm of the stream that already holds the mixer's output
-      { const double nsrc = cb.n; HFWD(C_ACT, Td * (8.0 * S + nsrc * es), 0, flush()); }
+      { const double nsrc = cb.n + (s.hyb_postnorm ? 1 : 0); HFWD(C_ACT, Td * (8.0 * S + nsrc * es), 0, flush()); }      // post-norm models also write the next normed row
       sub = 1;
       if (!hyper && !s.hyb_postnorm) HFWD(C_NORM, Td * (4 + es), 0, layer_norm(e->hx, nullptr, L.norm2, T, 1.f));
     }
@@ -1001,7 +1001,7 @@ int hybrid_forward(kge_engine* e, int T, int B, int R, int max_blocks, const Ste
       }
       if (h.shared_ff > 0) { if (cb.n == 4) HFWD(C_ACT, Td * (8 + 4 * es), 0, flush_more()); add_src(e->obuf2, d, 1.f, L.s_sg ? e->gates32 : nullptr, 1); }
     }
-    { const double nsrc = cb.n; HFWD(C_ACT, Td * (8.0 * S + nsrc * es), 0, flush()); }
+    { const double nsrc = cb.n + (s.hyb_postnorm ? 1 : 0); HFWD(C_ACT, Td * (8.0 * S + nsrc * es), 0, flush()); }      // post-norm models also write the next normed row
     if (e->layer_dump_host && (int64_t)(i + 1) * T * d <= e->layer_dump_cap) {
       if (hyper) { if (int rc = stream_read(nullptr, nullptr, nullptr, nullptr, T, 1.f, e->y32)) return rc; }      // the sum of the streams
       KGE_CUDA_OK(cudaMemcpyAsync(e->layer_dump_host + (int64_t)i * T * d, hyper ? e->y32 : e->res32, (size_t)T * d * 4, cudaMemcpyDeviceToHost, st));

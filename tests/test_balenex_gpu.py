@@ -398,6 +398,20 @@ def test_tensor_core_head_sizes(kge, tmp_path, shape):
     check(lg[1:], wc[131:], "bfloat16", "a prompt piece that starts inside a page beside a single token", noise)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width,groups", [(512, 2), (256, 1), (1024, 8), (384, 3)])
+def test_wide_rows_and_groups(kge, tmp_path, dtype, width, groups):
+    """Wider rows in groups of 128, 256 and 512 columns through the norm of a sublayer's result, the residual sum and the next
+    norm, for both kinds of sublayer result (two normed sources, one plain source)."""
+    cfg = ob.make_config([ob.parallel_layer(ff=24), ob.attention_layer(ff=0), ob.attention_layer(ff=16)], width=width, groups=groups, vocab=64)
+    W = ob.make_weights(cfg, seed=24)
+    toks = prompt(cfg, 21, 38)
+    want = ob.forward(cfg, W, toks)
+    llm = make_engine(kge, tmp_path, cfg, W, dtype, tokens=64)
+    check(run_pieces(llm, 0, toks, [9, 1, 11]), want, dtype, "pieces", ob.bfloat16_noise(cfg, W, toks))
+    llm.close()
+
+
 def test_first_tokens(kge, tmp_path):
     cfg = full()
     W = ob.make_weights(cfg, seed=11)
